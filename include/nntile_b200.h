@@ -1,0 +1,226 @@
+/* nntile_b200 - B200 (sm_100a) kernels for NNTile's tiled scaled-dot-product
+ * attention path, behind a plain C ABI.
+ *
+ * Conventions shared by every entry point (they are those of the reference's
+ * nntile::kernel::<op>::cuda<T> functions, include/nntile/kernel/cuda.hh:85-120):
+ *   - the first argument is the CUDA stream (a cudaStream_t passed as void*);
+ *     work is only ENQUEUED on it, nothing synchronises;
+ *   - sizes are int64_t (NNTile's Index), scalars are float (NNTile's Scalar);
+ *   - all pointers are DEVICE pointers owned by the caller for the lifetime of
+ *     the enqueued work; the library allocates nothing;
+ *   - arrays are Fortran order (first index fastest), fp32 or bfloat16
+ *     (bit-compatible with nntile::bf16_t / __nv_bfloat16);
+ *   - the return value is a status: 0 = enqueued, negative = rejected before any
+ *     launch (see NNTILE_B200_E_*).  Nothing is thrown and nothing is printed.
+ *
+ * Every declaration cites the reference interface it replaces as file:line,
+ * relative to the reference tree (nntile/nntile v1.1.0).
+ */
+#ifndef NNTILE_B200_H
+#define NNTILE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NNTILE_B200_OK 0
+#define NNTILE_B200_E_BADARG (-1)   /* null pointer, negative or inconsistent size */
+#define NNTILE_B200_E_SHAPE (-2)    /* shape not supported by this entry point */
+#define NNTILE_B200_E_ALIGN (-3)    /* pointer not aligned as documented */
+#define NNTILE_B200_E_SCRATCH (-4)  /* caller-provided scratch/workspace too small */
+#define NNTILE_B200_E_LAUNCH (-5)   /* CUDA refused the launch (cudaGetLastError) */
+#define NNTILE_B200_E_DEVICE (-6)   /* device is not compute capability 10.x */
+
+typedef void *nntile_b200_stream_t; /* cudaStream_t */
+
+/* Library version (major*10000 + minor*100 + patch) and status text. */
+int nntile_b200_version(void);
+const char *nntile_b200_status_string(int status);
+/* Number of CUDA kernels this library has launched in this process so far
+ * (memsets are not kernels).  No reference counterpart: a measurement aid. */
+unsigned long long nntile_b200_launch_count(void);
+
+/* ---------------------------------------------------------------------------
+ * Unfused chain (the "vanilla" path of nntile.layer.Sdpa)
+ * ------------------------------------------------------------------------- */
+
+/* if(!mask[i]) data[i,:] = val, data is nrows-by-ncols.
+ * Replaces nntile::kernel::mask_scalar::cuda<T>,
+ * include/nntile/kernel/mask_scalar/cuda.hh:25, src/kernel/mask_scalar/cuda.cu:21-110. */
+int nntile_b200_mask_scalar_fp32(nntile_b200_stream_t stream, int64_t nrows,
+        int64_t ncols, const uint8_t *mask, float val, float *data);
+int nntile_b200_mask_scalar_bf16(nntile_b200_stream_t stream, int64_t nrows,
+        int64_t ncols, const uint8_t *mask, float val, void *data);
+
+/* Running (max, sum exp(x-max)) of every fibre src[i,:,j] of an m-by-k-by-n array,
+ * merged into the interleaved 2-by-m-by-n `maxsumexp`; infinite entries are
+ * ignored, a stored sum of zero means "empty".
+ * Replaces nntile::kernel::maxsumexp::cuda<T>,
+ * include/nntile/kernel/maxsumexp/cuda.hh:25, src/kernel/maxsumexp/cuda.cu:22-323. */
+int nntile_b200_maxsumexp_fp32(nntile_b200_stream_t stream, int64_t m, int64_t n,
+        int64_t k, const float *src, float *maxsumexp);
+int nntile_b200_maxsumexp_bf16(nntile_b200_stream_t stream, int64_t m, int64_t n,
+        int64_t k, const void *src, void *maxsumexp);
+
+/* dst[i,l,j] = alpha*exp(dst[i,l,j]-max[i,j])/sum[i,j]; infinite entries -> 0.
+ * Replaces nntile::kernel::softmax_inplace::cuda<T>,
+ * include/nntile/kernel/softmax_inplace/cuda.hh:25, src/kernel/softmax_inplace/cuda.cu:22-181. */
+int nntile_b200_softmax_inplace_fp32(nntile_b200_stream_t stream, int64_t m,
+        int64_t n, int64_t k, const float *maxsumexp, float alpha, float *dst);
+int nntile_b200_softmax_inplace_bf16(nntile_b200_stream_t stream, int64_t m,
+        int64_t n, int64_t k, const void *maxsumexp, float alpha, void *dst);
+
+/* dst[i,j] = beta*dst[i,j] + alpha*sum_l src1[i,l,j]*src2[i,l,j]; beta==0 does not
+ * read dst.  Replaces nntile::kernel::sumprod_slice::cuda<T>,
+ * include/nntile/kernel/sumprod_slice/cuda.hh:25, src/kernel/sumprod_slice/cuda.cu:22-214. */
+int nntile_b200_sumprod_slice_fp32(nntile_b200_stream_t stream, int64_t m,
+        int64_t n, int64_t k, float alpha, const float *src1, const float *src2,
+        float beta, float *dst);
+int nntile_b200_sumprod_slice_bf16(nntile_b200_stream_t stream, int64_t m,
+        int64_t n, int64_t k, float alpha, const void *src1, const void *src2,
+        float beta, void *dst);
+
+/* dst[i,l,j] = beta*dst[i,l,j] + alpha*src[i,j].
+ * Replaces nntile::kernel::add_slice_inplace::cuda<T>,
+ * include/nntile/kernel/add_slice_inplace/cuda.hh:25, src/kernel/add_slice_inplace/cuda.cu:22-158. */
+int nntile_b200_add_slice_inplace_fp32(nntile_b200_stream_t stream, int64_t m,
+        int64_t n, int64_t k, float alpha, const float *src, float beta, float *dst);
+int nntile_b200_add_slice_inplace_bf16(nntile_b200_stream_t stream, int64_t m,
+        int64_t n, int64_t k, float alpha, const void *src, float beta, void *dst);
+
+/* dst = alpha*src*dst.  Replaces nntile::kernel::multiply_inplace::cuda<T>,
+ * include/nntile/kernel/multiply_inplace/cuda.hh:25, src/kernel/multiply_inplace/cuda.cu:21-76. */
+int nntile_b200_multiply_inplace_fp32(nntile_b200_stream_t stream, int64_t nelems,
+        float alpha, const float *src, float *dst);
+int nntile_b200_multiply_inplace_bf16(nntile_b200_stream_t stream, int64_t nelems,
+        float alpha, const void *src, void *dst);
+
+/* dst = alpha*src + beta*dst.  Replaces nntile::kernel::add_inplace::cuda<T>,
+ * include/nntile/kernel/add_inplace/cuda.hh:25. */
+int nntile_b200_add_inplace_fp32(nntile_b200_stream_t stream, int64_t nelems,
+        float alpha, const float *src, float beta, float *dst);
+int nntile_b200_add_inplace_bf16(nntile_b200_stream_t stream, int64_t nelems,
+        float alpha, const void *src, float beta, void *dst);
+
+/* dst[i] = val (fp32) and dst bytes = 0: the prologue of the fused forward
+ * (lse = -inf, A = 0; wrappers/python/nntile/layer/sdpa.py:538-539).
+ * Replace nntile::kernel::fill::cuda<fp32_t>, include/nntile/kernel/fill/cuda.hh:24,
+ * and the clear codelet, src/starpu/clear.cc. */
+int nntile_b200_fill_fp32(nntile_b200_stream_t stream, int64_t nelems, float val,
+        float *dst);
+int nntile_b200_clear(nntile_b200_stream_t stream, int64_t nbytes, void *dst);
+
+/* Merge a partial attention result (src_lse[seq*batch], src_attn[head, seq*batch])
+ * into the running one by log-sum-exp weights; rows whose incoming lse is not
+ * finite are left untouched.
+ * Replaces nntile::kernel::accumulate_attn_output::cuda<T>,
+ * include/nntile/kernel/accumulate_attn_output/cuda.hh:25,
+ * src/kernel/accumulate_attn_output/cuda.cu:28-135. */
+int nntile_b200_accumulate_attn_output_fp32(nntile_b200_stream_t stream,
+        int64_t head, int64_t seq, int64_t batch, const float *src_lse,
+        const float *src_attn, float *dst_lse, float *dst_attn);
+int nntile_b200_accumulate_attn_output_bf16(nntile_b200_stream_t stream,
+        int64_t head, int64_t seq, int64_t batch, const float *src_lse,
+        const void *src_attn, float *dst_lse, void *dst_attn);
+
+/* ---------------------------------------------------------------------------
+ * Fused flash SDPA, one (Q tile, K/V tile) task
+ * ------------------------------------------------------------------------- */
+
+/* Forward: (lse, A) <- merge((lse, A), SDPA(Q, K, V, bias=mask, scale=1/sqrt(head))).
+ * Per batch entry K, Q, V, A are row-major [seq][head] matrices, `batch` of them
+ * back to back; mask is the additive bias [seq_q][seq_k] row major in bf16
+ * (0 = keep, -inf = drop, any finite value allowed); lse is fp32 [batch][seq].
+ * The caller initialises lse = -inf, A = 0 before the first K/V tile of a Q tile.
+ * scratch_lse (seq*batch floats) and scratch_A (seq*head*batch bf16) are the two
+ * scratch buffers the reference's tile layer hands to every task; they may be
+ * overwritten with anything.  All pointers 16-byte aligned.
+ * Pointer order and semantics are those of
+ * nntile::kernel::flash_sdpa_fwd_cudnn::execute_graph<bf16_t>,
+ * include/nntile/kernel/flash_sdpa_fwd_cudnn/cuda.hh:37-76,
+ * src/kernel/flash_sdpa_fwd_cudnn/cuda.cc:145-202 (cuDNN graph + merge), with the
+ * cudnnHandle_t/graph pair replaced by the stream. */
+int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q,
+        const void *mask, float *scratch_lse, const void *V, void *scratch_A,
+        float *lse, void *A);
+
+/* Backward: dK, dQ, dV += gradients of one (Q tile, K/V tile) pair computed from
+ * the GIVEN A (final output) and lse (final log-sum-exp) of the Q tile.
+ * The three scratch buffers (each seq*head*batch bf16) may be overwritten.
+ * Pointer order and semantics are those of
+ * nntile::kernel::flash_sdpa_bwd_cudnn::execute_graph<bf16_t>,
+ * include/nntile/kernel/flash_sdpa_bwd_cudnn/cuda.hh:29-59,
+ * src/kernel/flash_sdpa_bwd_cudnn/cuda.cc:171-218; no separate workspace. */
+int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q, const void *V,
+        const void *A, const void *dA, const void *mask, const float *lse,
+        void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ,
+        void *dV);
+
+/* Which implementation the two entry points above pick for a shape:
+ * 2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel, 0 = rejected. */
+int nntile_b200_flash_sdpa_fwd_path(int64_t seq, int64_t head, int64_t batch);
+int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_t batch);
+
+/* ---------------------------------------------------------------------------
+ * Decode: one new query token against a KV cache, split over the cache length
+ * ------------------------------------------------------------------------- */
+
+/* out[head, 1, batch, group, kv_heads] = softmax(q.K^T/sqrt(head)) V over the first
+ * `length` cache positions, reading the un-replicated cache once for all `group`
+ * query heads of a KV head.  q/out: bf16 [head, 1, batch, group, kv_heads];
+ * Kcache/Vcache: bf16 [head, max_seq, batch, kv_heads] (the reference's cache
+ * layout, include/nntile/graph/kv_cache.hh:38-39); lse_out: optional fp32
+ * [batch, group, kv_heads] (may be NULL).  `workspace` must hold at least
+ * nntile_b200_decode_sdpa_workspace_bytes(...) bytes, 16-byte aligned.
+ * Replaces the chain the reference runs for a non-empty cache (cache copy + K/V
+ * replication + gemm/maxsumexp/softmax_inplace/gemm with one query position,
+ * wrappers/python/nntile/model/llama_attention.py:533-616, 672-676,
+ * wrappers/python/nntile/layer/sdpa.py:238-306). */
+int nntile_b200_decode_sdpa_bf16(nntile_b200_stream_t stream, int64_t head,
+        int64_t max_seq, int64_t length, int64_t batch, int64_t group,
+        int64_t kv_heads, const void *q, const void *Kcache, const void *Vcache,
+        void *out, float *lse_out, void *workspace, size_t workspace_bytes);
+size_t nntile_b200_decode_sdpa_workspace_bytes(int64_t head, int64_t length,
+        int64_t batch, int64_t group, int64_t kv_heads);
+
+/* ---------------------------------------------------------------------------
+ * Tensor level: the tile loops of the fused path
+ * ------------------------------------------------------------------------- */
+
+/* K, Q, V, A (and dA, dK, dQ, dV) are tiled tensors of `shape` =
+ * [head, seq, batch, group, kv_heads] cut into tiles of `basetile`; every tile is
+ * a separate Fortran-order device buffer and `*_tiles[i]` is tile i in Fortran
+ * order of the tile grid.  mask is [seq, seq] tiled [basetile[1], basetile[1]]
+ * (tile (k, q) at k + q*nseq_tiles), lse is [seq, batch, group, kv_heads] tiled
+ * like A without the head axis.  For every output tile, one tile task per K/V
+ * sequence tile is enqueued in order (fully masked pairs included, as in the
+ * reference).  The caller runs the prologue (lse = -inf, A = 0) for the forward
+ * and provides `scratch` of nntile_b200_tensor_flash_sdpa_scratch_bytes(basetile)
+ * bytes, 256-byte aligned, reused by every task.
+ * Replace nntile::tensor::flash_sdpa_fwd_cudnn_async<bf16_t>,
+ * src/tensor/flash_sdpa_fwd_cudnn.cc:211-279 (+ src/tile/flash_sdpa_fwd_cudnn.cc:161-196)
+ * and nntile::tensor::flash_sdpa_bwd_cudnn_async<bf16_t>,
+ * src/tensor/flash_sdpa_bwd_cudnn.cc:154-246 (+ src/tile/flash_sdpa_bwd_cudnn.cc:90-136). */
+int nntile_b200_tensor_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *mask_tiles,
+        float *const *lse_tiles, const void *const *V_tiles, void *const *A_tiles,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_tensor_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *V_tiles,
+        const void *const *A_tiles, const void *const *dA_tiles,
+        const void *const *mask_tiles, const float *const *lse_tiles,
+        void *const *dK_tiles, void *const *dQ_tiles, void *const *dV_tiles,
+        void *scratch, size_t scratch_bytes);
+size_t nntile_b200_tensor_flash_sdpa_scratch_bytes(const int64_t *basetile);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNTILE_B200_H */

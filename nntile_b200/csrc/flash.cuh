@@ -1,0 +1,29 @@
+// Internal interface between the C entry points of the fused SDPA tile tasks
+// and the kernels that implement them.
+#pragma once
+#include "common.cuh"
+
+namespace nb200 {
+
+// Generic CUDA-core kernels (flash_generic.cu): any seq, head <= 256.
+int flash_fwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
+        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A);
+int flash_bwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
+        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
+        const float *lse, float *delta, bf16 *dK, bf16 *dQ, bf16 *dV);
+int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const bf16 *A, const bf16 *dA,
+        float *delta);
+
+// tcgen05 / TMEM / TMA kernels (flash_fwd_sm100.cu, flash_bwd_sm100.cu):
+// head in {64, 128}, seq a multiple of 128.
+bool flash_fwd_sm100_supports(Index seq, Index head, Index batch);
+int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
+        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A,
+        void *scratch, size_t scratch_bytes);
+bool flash_bwd_sm100_supports(Index seq, Index head, Index batch);
+int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
+        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
+        const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV,
+        bf16 *dK, bf16 *dQ, bf16 *dV);
+
+} // namespace nb200

@@ -1,0 +1,88 @@
+// C entry points of the fused flash-SDPA tile tasks: argument checks and the
+// choice between the tcgen05 kernels and the generic CUDA kernels.  Both are
+// device code; there is no host fallback.
+#include "flash.cuh"
+
+using namespace nb200;
+
+static int check_common(int64_t seq, int64_t head, int64_t batch)
+{
+    if(seq < 0 || head < 0 || batch < 0) return NNTILE_B200_E_BADARG;
+    if(head > 256 || seq > (int64_t)1 << 24) return NNTILE_B200_E_SHAPE;
+    return NNTILE_B200_OK;
+}
+
+extern "C" int nntile_b200_flash_sdpa_fwd_path(int64_t seq, int64_t head, int64_t batch)
+{
+    if(check_common(seq, head, batch) != NNTILE_B200_OK) return 0;
+    return flash_fwd_sm100_supports(seq, head, batch) ? 2 : 1;
+}
+
+extern "C" int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_t batch)
+{
+    if(check_common(seq, head, batch) != NNTILE_B200_OK || head < 2) return 0;
+    return flash_bwd_sm100_supports(seq, head, batch) ? 2 : 1;
+}
+
+extern "C" int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q, const void *mask,
+        float *scratch_lse, const void *V, void *scratch_A, float *lse, void *A)
+{
+    int st = check_common(seq, head, batch);
+    if(st != NNTILE_B200_OK) return st;
+    if(seq == 0 || head == 0 || batch == 0) return NNTILE_B200_OK;
+    if(!K || !Q || !mask || !V || !lse || !A) return NNTILE_B200_E_BADARG;
+    (void)scratch_lse;
+    if(flash_fwd_sm100_supports(seq, head, batch))
+    {
+        if(!scratch_A) return NNTILE_B200_E_BADARG;
+        if(!aligned16(K) || !aligned16(Q) || !aligned16(V) || !aligned16(A)
+                || !aligned16(mask) || !aligned16(scratch_A))
+        {
+            return NNTILE_B200_E_ALIGN;
+        }
+        return flash_fwd_sm100(as_stream(stream), seq, head, batch, (const bf16 *)K,
+                (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A,
+                scratch_A, (size_t)seq*head*batch*sizeof(bf16));
+    }
+    return flash_fwd_generic(as_stream(stream), seq, head, batch, (const bf16 *)K,
+            (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A);
+}
+
+extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q, const void *V,
+        const void *A, const void *dA, const void *mask, const float *lse,
+        void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ, void *dV)
+{
+    int st = check_common(seq, head, batch);
+    if(st != NNTILE_B200_OK) return st;
+    if(seq == 0 || head == 0 || batch == 0) return NNTILE_B200_OK;
+    if(!K || !Q || !V || !A || !dA || !mask || !lse || !dK || !dQ || !dV
+            || !scratch_dK || !scratch_dQ || !scratch_dV)
+    {
+        return NNTILE_B200_E_BADARG;
+    }
+    // delta (seq*batch floats) lives in scratch_dV: needs head >= 2
+    if(head < 2) return NNTILE_B200_E_SHAPE;
+    if(!aligned16(scratch_dV) || !aligned16(scratch_dQ) || !aligned16(scratch_dK))
+    {
+        return NNTILE_B200_E_ALIGN;
+    }
+    if(flash_bwd_sm100_supports(seq, head, batch))
+    {
+        if(!aligned16(K) || !aligned16(Q) || !aligned16(V) || !aligned16(A)
+                || !aligned16(dA) || !aligned16(mask) || !aligned16(dK)
+                || !aligned16(dQ) || !aligned16(dV))
+        {
+            return NNTILE_B200_E_ALIGN;
+        }
+        return flash_bwd_sm100(as_stream(stream), seq, head, batch, (const bf16 *)K,
+                (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
+                (const bf16 *)mask, lse, scratch_dK, scratch_dQ, scratch_dV,
+                (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV);
+    }
+    return flash_bwd_generic(as_stream(stream), seq, head, batch, (const bf16 *)K,
+            (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
+            (const bf16 *)mask, lse, (float *)scratch_dV, (bf16 *)dK, (bf16 *)dQ,
+            (bf16 *)dV);
+}

@@ -1,0 +1,150 @@
+"""Kernel-level operations on torch CUDA tensors.
+
+Each function mirrors one ``nntile::kernel::<op>::cuda<T>`` entry point of the
+reference (same name, same argument order, sizes first) and only enqueues work
+on the current torch stream.  Tensors are raw buffers: what matters is their
+memory, which must hold the Fortran-order array the sizes describe (a Fortran
+array of shape [a, b, c] is a contiguous torch tensor of shape (c, b, a)).
+dtype float32 selects the fp32 kernels, bfloat16 the bf16 ones.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise ValueError("nntile_b200 ops need CUDA tensors (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError("nntile_b200 ops need contiguous buffers")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _sfx(t) -> str:
+    if t.dtype == torch.float32:
+        return "fp32"
+    if t.dtype == torch.bfloat16:
+        return "bf16"
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _call(name, *args):
+    fn = getattr(_lib.load(), name)
+    _lib.check(name, fn(*args))
+
+
+def mask_scalar(nrows, ncols, mask, val, data):
+    """mask: uint8/bool buffer of nrows entries (true = keep)."""
+    if mask.dtype == torch.bool:
+        mask = mask.view(torch.uint8)
+    _call(f"nntile_b200_mask_scalar_{_sfx(data)}", _stream(), nrows, ncols, _ptr(mask),
+          float(val), _ptr(data))
+
+
+def maxsumexp(m, n, k, src, maxsumexp_):
+    _call(f"nntile_b200_maxsumexp_{_sfx(src)}", _stream(), m, n, k, _ptr(src), _ptr(maxsumexp_))
+
+
+def softmax_inplace(m, n, k, maxsumexp_, alpha, dst):
+    _call(f"nntile_b200_softmax_inplace_{_sfx(dst)}", _stream(), m, n, k, _ptr(maxsumexp_),
+          float(alpha), _ptr(dst))
+
+
+def sumprod_slice(m, n, k, alpha, src1, src2, beta, dst):
+    _call(f"nntile_b200_sumprod_slice_{_sfx(dst)}", _stream(), m, n, k, float(alpha),
+          _ptr(src1), _ptr(src2), float(beta), _ptr(dst))
+
+
+def add_slice_inplace(m, n, k, alpha, src, beta, dst):
+    _call(f"nntile_b200_add_slice_inplace_{_sfx(dst)}", _stream(), m, n, k, float(alpha),
+          _ptr(src), float(beta), _ptr(dst))
+
+
+def multiply_inplace(nelems, alpha, src, dst):
+    _call(f"nntile_b200_multiply_inplace_{_sfx(dst)}", _stream(), nelems, float(alpha),
+          _ptr(src), _ptr(dst))
+
+
+def add_inplace(nelems, alpha, src, beta, dst):
+    _call(f"nntile_b200_add_inplace_{_sfx(dst)}", _stream(), nelems, float(alpha), _ptr(src),
+          float(beta), _ptr(dst))
+
+
+def fill(val, dst):
+    _call("nntile_b200_fill_fp32", _stream(), dst.numel(), float(val), _ptr(dst))
+
+
+def clear(dst):
+    _call("nntile_b200_clear", _stream(), dst.numel()*dst.element_size(), _ptr(dst))
+
+
+def accumulate_attn_output(head, seq, batch, src_lse, src_attn, dst_lse, dst_attn):
+    _call(f"nntile_b200_accumulate_attn_output_{_sfx(dst_attn)}", _stream(), head, seq, batch,
+          _ptr(src_lse), _ptr(src_attn), _ptr(dst_lse), _ptr(dst_attn))
+
+
+def gemm(transA, transB, m, n, k, batch, alpha, A, B, beta, C):
+    """Batched column-major C = alpha*op(A)*op(B) + beta*C with packed leading
+    dimensions - the contract of nntile::kernel::cublas::gemm<T>
+    (src/kernel/cublas.cc:35-164).  A library GEMM in the reference and here:
+    cuBLAS through torch.baddbmm, fp32 accumulation, no TF32."""
+    # a column-major p-by-q matrix is a row-major (q, p) torch matrix
+    a = A.view(batch, m, k) if transA else A.view(batch, k, m)
+    b = B.view(batch, k, n) if transB else B.view(batch, n, k)
+    c = C.view(batch, n, m)
+    # C^T = op(B)^T op(A)^T
+    bt = b.transpose(1, 2) if transB else b
+    at = a.transpose(1, 2) if transA else a
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        if beta == 0.0:
+            torch.bmm(bt, at, out=c)
+            if alpha != 1.0:
+                c.mul_(alpha)
+        else:
+            torch.baddbmm(c, bt, at, beta=float(beta), alpha=float(alpha), out=c)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def flash_sdpa_fwd(seq, head, batch, K, Q, mask, scratch_lse, V, scratch_A, lse, A):
+    """Pointer order of flash_sdpa_fwd_cudnn::execute_graph."""
+    _call("nntile_b200_flash_sdpa_fwd_bf16", _stream(), seq, head, batch, _ptr(K), _ptr(Q),
+          _ptr(mask), _ptr(scratch_lse), _ptr(V), _ptr(scratch_A), _ptr(lse), _ptr(A))
+
+
+def flash_sdpa_bwd(seq, head, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scratch_dQ,
+                   scratch_dV, dK, dQ, dV):
+    """Pointer order of flash_sdpa_bwd_cudnn::execute_graph."""
+    _call("nntile_b200_flash_sdpa_bwd_bf16", _stream(), seq, head, batch, _ptr(K), _ptr(Q),
+          _ptr(V), _ptr(A), _ptr(dA), _ptr(mask), _ptr(lse), _ptr(scratch_dK),
+          _ptr(scratch_dQ), _ptr(scratch_dV), _ptr(dK), _ptr(dQ), _ptr(dV))
+
+
+def flash_sdpa_path(seq, head, batch, backward=False) -> int:
+    lib = _lib.load()
+    fn = lib.nntile_b200_flash_sdpa_bwd_path if backward else lib.nntile_b200_flash_sdpa_fwd_path
+    return int(fn(seq, head, batch))
+
+
+def decode_workspace_bytes(head, length, batch, group, kv_heads) -> int:
+    return int(_lib.load().nntile_b200_decode_sdpa_workspace_bytes(head, length, batch, group,
+                                                                   kv_heads))
+
+
+def decode_sdpa(head, max_seq, length, batch, group, kv_heads, q, Kcache, Vcache, out,
+                lse_out, workspace):
+    _call("nntile_b200_decode_sdpa_bf16", _stream(), head, max_seq, length, batch, group,
+          kv_heads, _ptr(q), _ptr(Kcache), _ptr(Vcache), _ptr(out), _ptr(lse_out),
+          _ptr(workspace), workspace.numel()*workspace.element_size())

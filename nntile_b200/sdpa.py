@@ -1,0 +1,220 @@
+"""Host-side mirror of ``nntile.layer.Sdpa`` for the path (reference:
+wrappers/python/nntile/layer/sdpa.py).
+
+Tensors are torch CUDA buffers holding NNTile's Fortran-order arrays: an NNTile
+tensor of shape [head, seq, batch, group, kv_heads] is a contiguous torch tensor
+of shape (kv_heads, group, batch, seq, head).  ``from_fortran`` / ``to_fortran``
+convert from and to numpy Fortran arrays (bf16 as uint16 bit patterns).
+
+``Sdpa`` issues the same operations in the same order as the reference layer:
+the unfused chain (gemm -> mask_scalar -> maxsumexp -> softmax_inplace -> gemm
+and its backward, sdpa.py:407-455, 595-698) or the fused tile tasks (fill/clear
+prologue + flash forward, flash backward, sdpa.py:533-593) with the reference's
+tile loops run by the C library.
+"""
+from __future__ import annotations
+
+import ctypes
+import itertools
+import math
+
+import numpy as np
+import torch
+
+from . import _lib, ops
+
+
+def from_fortran(arr: np.ndarray, device="cuda") -> torch.Tensor:
+    """numpy Fortran array (float32, or uint16 = bf16 bits) -> torch buffer."""
+    a = np.asfortranarray(arr)
+    if a.dtype == np.uint16:
+        return torch.from_numpy(a.T.view(np.int16).copy()).view(torch.bfloat16).to(device)
+    if a.dtype == np.bool_:
+        return torch.from_numpy(a.T.copy()).to(device)
+    return torch.from_numpy(a.T.copy()).to(device)
+
+
+def to_fortran(t: torch.Tensor) -> np.ndarray:
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return np.asfortranarray(t.view(torch.int16).numpy().view(np.uint16).T)
+    return np.asfortranarray(t.numpy().T)
+
+
+def sdpa_scale(head_size: int) -> float:
+    """sdpa.py:149."""
+    return float(np.float32(1.0)/np.sqrt(np.float32(head_size)))
+
+
+class TiledBuffer:
+    """A tensor cut into separately stored Fortran-order tiles, the storage model
+    of nntile::tensor::Tensor (include/nntile/tensor/tensor.hh).  `shape` and
+    `basetile` are in NNTile (Fortran) order."""
+
+    def __init__(self, full: torch.Tensor, basetile):
+        self.shape = tuple(reversed(full.shape))
+        self.basetile = tuple(int(b) for b in basetile)
+        self.grid = tuple(-(-s//b) for s, b in zip(self.shape, self.basetile))
+        self.dtype = full.dtype
+        self.tiles = []
+        # Fortran order of the tile grid: first index fastest
+        for idx in itertools.product(*(range(g) for g in reversed(self.grid))):
+            idx = tuple(reversed(idx))
+            self.tiles.append(full[self._slices(idx)].contiguous())
+
+    def _slices(self, idx):
+        sl = [slice(i*b, min((i + 1)*b, s)) for i, b, s in zip(idx, self.basetile, self.shape)]
+        return tuple(reversed(sl))
+
+    def pointers(self):
+        arr = (ctypes.c_void_p*len(self.tiles))(*[t.data_ptr() for t in self.tiles])
+        return arr
+
+    def gather(self) -> torch.Tensor:
+        out = torch.empty(tuple(reversed(self.shape)), dtype=self.dtype,
+                          device=self.tiles[0].device)
+        for n, idx in enumerate(itertools.product(*(range(g) for g in reversed(self.grid)))):
+            out[self._slices(tuple(reversed(idx)))] = self.tiles[n]
+        return out
+
+
+def _i64arr(vals):
+    return (ctypes.c_int64*len(vals))(*[int(v) for v in vals])
+
+
+def flash_sdpa_fwd_async(K, Q, mask, lse, V, A, seq_tile=None, batch_tile=None):
+    """nntile.functions.flash_sdpa_fwd_cudnn_async on whole tensors: cuts them into
+    tiles like the reference's traits do, runs the C tensor-level loops, gathers A
+    and lse back in place.  K, Q, V, A: (H, G, B, S, D) bf16; mask: additive
+    (Sq, Sk) bf16 buffer = Fortran [Sk, Sq]; lse: (H, G, B, S) fp32."""
+    H, G, B, S, D = Q.shape
+    seq_tile = seq_tile or S
+    bt = tuple(batch_tile or (B, G, H))
+    base5 = (D, seq_tile) + bt
+    tK, tQ, tV, tA = (TiledBuffer(x, base5) for x in (K, Q, V, A))
+    tM = TiledBuffer(mask, (seq_tile, seq_tile))
+    tL = TiledBuffer(lse, (seq_tile,) + bt)
+    lib = _lib.load()
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(_i64arr(base5))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
+    keep = [tK.pointers(), tQ.pointers(), tM.pointers(), tL.pointers(), tV.pointers(),
+            tA.pointers()]
+    st = lib.nntile_b200_tensor_flash_sdpa_fwd_bf16(
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), _i64arr((D, S, B, G, H)),
+        _i64arr(base5), *[ctypes.cast(p, ctypes.POINTER(ctypes.c_void_p)) for p in keep],
+        ctypes.c_void_p(scratch.data_ptr()), nbytes)
+    _lib.check("nntile_b200_tensor_flash_sdpa_fwd_bf16", st)
+    A.copy_(tA.gather())
+    lse.copy_(tL.gather())
+
+
+def flash_sdpa_bwd_async(K, Q, V, A, dA, mask, lse, dK, dQ, dV, seq_tile=None,
+                         batch_tile=None):
+    """nntile.functions.flash_sdpa_bwd_cudnn_async on whole tensors."""
+    H, G, B, S, D = Q.shape
+    seq_tile = seq_tile or S
+    bt = tuple(batch_tile or (B, G, H))
+    base5 = (D, seq_tile) + bt
+    tK, tQ, tV, tA, tdA, tdK, tdQ, tdV = (TiledBuffer(x, base5)
+                                          for x in (K, Q, V, A, dA, dK, dQ, dV))
+    tM = TiledBuffer(mask, (seq_tile, seq_tile))
+    tL = TiledBuffer(lse, (seq_tile,) + bt)
+    lib = _lib.load()
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(_i64arr(base5))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
+    keep = [t.pointers() for t in (tK, tQ, tV, tA, tdA, tM, tL, tdK, tdQ, tdV)]
+    st = lib.nntile_b200_tensor_flash_sdpa_bwd_bf16(
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), _i64arr((D, S, B, G, H)),
+        _i64arr(base5), *[ctypes.cast(p, ctypes.POINTER(ctypes.c_void_p)) for p in keep],
+        ctypes.c_void_p(scratch.data_ptr()), nbytes)
+    _lib.check("nntile_b200_tensor_flash_sdpa_bwd_bf16", st)
+    dK.copy_(tdK.gather())
+    dQ.copy_(tdQ.gather())
+    dV.copy_(tdV.gather())
+
+
+class Sdpa:
+    """Mirror of nntile.layer.Sdpa on single-tile tensors (or, for the fused
+    path, tensors tiled along sequence and batch axes).
+
+    q, k, v: (H, G, B, S, D) buffers.  ``mask``: for the unfused chain a bool
+    (Sq, Sk) buffer = Fortran [Sk, Sq] (true = keep); for the fused path the
+    additive mask in the tensors' dtype (0 / -inf), as sdpa.py:457-531 prepares.
+    """
+
+    def __init__(self, q, k, v, mask=None, flash_attention=False, seq_tile=None,
+                 batch_tile=None):
+        self.q, self.k, self.v, self.mask = q, k, v, mask
+        self.flash_attention = flash_attention
+        self.seq_tile, self.batch_tile = seq_tile, batch_tile
+        H, G, B, S, D = q.shape
+        self.head, self.n_seq = D, S
+        self.n_seq_k = k.shape[3]
+        self.batch = H*G*B
+        self.scale = sdpa_scale(D)
+        self.val = -math.inf
+        dev, dt = q.device, q.dtype
+        self.y = torch.zeros_like(q)
+        if flash_attention:
+            if dt != torch.bfloat16:
+                raise TypeError("the fused path takes bf16 only (fp32 is rejected by the "
+                                "reference as well, flash_sdpa_fwd_cudnn/cuda.cc:60-63)")
+            self.flash_logsumexp = torch.empty((H, G, B, S), dtype=torch.float32, device=dev)
+            if mask is None:
+                self.mask = torch.zeros((S, S), dtype=dt, device=dev)
+        else:
+            self.attn = torch.empty((H, G, B, S, self.n_seq_k), dtype=dt, device=dev)
+            self.attn_maxsumexp = torch.empty((H, G, B, S, 2), dtype=dt, device=dev)
+            self.attn_sumprod_slice = torch.empty((H, G, B, S), dtype=dt, device=dev)
+
+    # ---- forward ----------------------------------------------------------
+    def forward_async(self):
+        if self.flash_attention:
+            ops.fill(-math.inf, self.flash_logsumexp)          # sdpa.py:538
+            ops.clear(self.y)                                   # sdpa.py:539
+            flash_sdpa_fwd_async(self.k, self.q, self.mask, self.flash_logsumexp, self.v,
+                                 self.y, self.seq_tile, self.batch_tile)
+            return self.y
+        D, Sq, Sk, nb = self.head, self.n_seq, self.n_seq_k, self.batch
+        ops.gemm(True, False, Sk, Sq, D, nb, self.scale, self.k, self.q, 0.0, self.attn)
+        ops.clear(self.attn_maxsumexp)
+        if self.mask is not None:
+            ops.mask_scalar(Sk*Sq, nb, self.mask, self.val, self.attn)
+        ops.maxsumexp(1, Sq*nb, Sk, self.attn, self.attn_maxsumexp)
+        ops.softmax_inplace(1, Sq*nb, Sk, self.attn_maxsumexp, 1.0, self.attn)
+        ops.gemm(False, False, D, Sq, Sk, nb, 1.0, self.v, self.attn, 0.0, self.y)
+        return self.y
+
+    # ---- backward: dq, dk, dv are INCREMENTED, as in the reference -----------
+    def backward_async(self, dy, dq, dk, dv):
+        if self.flash_attention:
+            flash_sdpa_bwd_async(self.k, self.q, self.v, self.y, dy, self.mask,
+                                 self.flash_logsumexp, dk, dq, dv, self.seq_tile,
+                                 self.batch_tile)
+            return
+        D, Sq, Sk, nb = self.head, self.n_seq, self.n_seq_k, self.batch
+        dattn = torch.empty_like(self.attn)
+        ops.gemm(True, False, Sk, Sq, D, nb, 1.0, self.v, dy, 0.0, dattn)
+        ops.gemm(False, True, D, Sk, Sq, nb, 1.0, dy, self.attn, 1.0, dv)
+        ops.sumprod_slice(1, Sq*nb, D, 1.0, self.y, dy, 0.0, self.attn_sumprod_slice)
+        ops.add_slice_inplace(1, Sq*nb, Sk, -1.0, self.attn_sumprod_slice, 1.0, dattn)
+        ops.multiply_inplace(dattn.numel(), 1.0, self.attn, dattn)
+        if self.mask is not None:
+            ops.mask_scalar(Sk*Sq, nb, self.mask, 0.0, dattn)
+        ops.gemm(False, True, D, Sk, Sq, nb, self.scale, self.q, dattn, 1.0, dk)
+        ops.gemm(False, False, D, Sq, Sk, nb, self.scale, self.k, dattn, 1.0, dq)
+
+
+def decode_sdpa(q, Kcache, Vcache, length=None, out=None, lse_out=None, workspace=None):
+    """One new token against the cache.  q: (H, G, B, 1, D) bf16; caches:
+    (H, B, L, D) bf16 = Fortran [D, L, B, H].  Returns out shaped like q."""
+    H, G, B, one, D = q.shape
+    L = Kcache.shape[2]
+    length = L if length is None else int(length)
+    if out is None:
+        out = torch.empty_like(q)
+    if workspace is None:
+        n = ops.decode_workspace_bytes(D, length, B, G, H)
+        workspace = torch.empty(max(n, 16), dtype=torch.uint8, device=q.device)
+    ops.decode_sdpa(D, L, length, B, G, H, q, Kcache, Vcache, out, lse_out, workspace)
+    return out

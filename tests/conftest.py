@@ -20,3 +20,13 @@ def golden():
     def load(name):
         return dict(np.load(os.path.join(GOLDEN, name)))
     return load
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)

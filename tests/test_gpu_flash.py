@@ -1,0 +1,229 @@
+"""GPU parity of the fused flash-SDPA tile tasks, called through the C ABI.
+
+Pins: (1) the reference kernel tests' own shapes, PRESET inputs, fp64 formulas
+and eps 1e-2 (tests/golden/flash_preset.npz, from
+tests/kernel/flash_sdpa_{fwd,bwd}_cudnn.cc); (2) the oracle's restatement of the
+reference's tiled path on seeded inputs, <= 2e-2 relative (bf16 storage, fp32
+accumulation - the path's stated bar); (3) the tensor-test property "K/V tiles
+streamed through many tasks == one big tile"; (4) inputs bit-unchanged;
+(5) accumulate-into-output contracts (lse merge, += of gradients)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from nntile_b200 import ops
+from nntile_b200.sdpa import Sdpa, flash_sdpa_bwd_async, flash_sdpa_fwd_async, from_fortran, to_fortran
+
+pytestmark = pytest.mark.gpu
+F = np.asfortranarray
+BF16_TOL = 2e-2
+
+
+def _mg():
+    p = os.path.join(os.path.dirname(__file__), "golden", "make_golden.py")
+    spec = importlib.util.spec_from_file_location("make_golden", p)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def dev(a):
+    return from_fortran(a)
+
+
+def bf(t):
+    return O.from_bf16(to_fortran(t))
+
+
+def causal_add(S, dtype=np.float32):
+    """Fortran [k, q] additive causal mask: -inf where k > q."""
+    k, q = np.meshgrid(np.arange(S), np.arange(S), indexing="ij")
+    return F(np.where(k > q, -np.inf, 0.0).astype(dtype))
+
+
+def run_fwd(Q, K, V, mask, seq_tile=None, batch_tile=None):
+    q, k, v, m = dev(Q), dev(K), dev(V), dev(mask)
+    H, G, B, S, D = q.shape
+    lse = torch.full((H, G, B, S), -np.inf, dtype=torch.float32, device="cuda")
+    A = torch.zeros_like(q)
+    flash_sdpa_fwd_async(k, q, m, lse, v, A, seq_tile, batch_tile)
+    torch.cuda.synchronize()
+    return A, lse, (q, k, v, m)
+
+
+FWD_CASES = [(16, 32, 1, True), (32, 64, 2, True), (32, 32, 2, False), (16, 64, 1, False)]
+BWD_CASES = [(64, 8, 1, True), (64, 32, 4, True), (64, 32, 1, False), (64, 8, 4, False)]
+
+
+@pytest.mark.parametrize("seq,head,batch,causal", FWD_CASES)
+def test_fwd_reference_kernel_test_cases(golden, seq, head, batch, causal):
+    mg, g = _mg(), golden("flash_preset.npz")
+    Q, K, V, mask = mg.preset_fwd(seq, head, batch, causal)
+    Qb, Kb, Vb = (O.to_bf16(mg._as5(x, head, seq, batch)) for x in (Q, K, V))
+    mkq = O.to_bf16(F(mask.T))
+    A, lse, ins = run_fwd(Qb, Kb, Vb, mkq)
+    tag = f"fwd_s{seq}_h{head}_b{batch}_{'causal' if causal else 'full'}"
+    assert O.rel_err(bf(A), g[tag + "_A"]) <= 1e-2
+    assert np.allclose(to_fortran(lse), g[tag + "_lse"], rtol=1e-2, atol=1e-6)
+    # inputs must come back bit-identical (tests/kernel/flash_sdpa_fwd_cudnn.cc:345-362)
+    for t, src in zip(ins, (Qb, Kb, Vb, mkq)):
+        assert np.array_equal(to_fortran(t), src)
+
+
+@pytest.mark.parametrize("seq,head,batch,causal", BWD_CASES)
+def test_bwd_reference_kernel_test_cases(golden, seq, head, batch, causal):
+    mg, g = _mg(), golden("flash_preset.npz")
+    Q, K, V, A, dA, lse, mask = mg.preset_bwd(seq, head, batch, causal)
+    Qb, Kb, Vb, Ab, dAb = (O.to_bf16(mg._as5(x, head, seq, batch)) for x in (Q, K, V, A, dA))
+    mkq = O.to_bf16(F(mask.T))
+    l4 = F(lse.reshape(batch, seq).T.reshape(seq, batch, 1, 1))
+    tag = f"bwd_s{seq}_h{head}_b{batch}_{'causal' if causal else 'full'}"
+    args = [dev(x) for x in (Kb, Qb, Vb, Ab, dAb, mkq, l4)]
+    for init in (0.0, 0.25):      # += contract, tests/tile/flash_sdpa_bwd_cudnn.cc:298-325
+        dK, dQ, dV = (torch.full_like(args[0], init) for _ in range(3))
+        flash_sdpa_bwd_async(*args, dK, dQ, dV)
+        torch.cuda.synchronize()
+        for got, key in ((dQ, "_dQ"), (dK, "_dK"), (dV, "_dV")):
+            assert O.rel_err(bf(got), init + g[tag + key]) <= 1e-2
+
+
+SEEDED = [
+    # (head, seq, batch, group, kv_heads, mask kind)
+    (64, 128, 2, 1, 2, "causal"),
+    (128, 128, 1, 2, 1, "causal"),
+    (64, 256, 1, 1, 3, "band"),
+    (128, 384, 1, 1, 2, "causal"),
+    (64, 128, 1, 1, 1, "none"),
+    (32, 80, 2, 1, 1, "causal"),      # ragged for the fast path: generic kernels
+    (128, 256, 2, 1, 1, "ragged"),    # finite biases and a fully masked query row
+]
+
+
+def make_mask(kind, S):
+    if kind == "causal":
+        return causal_add(S)
+    if kind == "none":
+        return F(np.zeros((S, S), np.float32))
+    i = np.arange(S)
+    if kind == "band":
+        return F(np.where(np.abs(i[:, None] - i[None, :]) <= 32, 0.0, -np.inf).astype(np.float32))
+    m = causal_add(S)
+    rng = np.random.default_rng(5)
+    m = np.where(np.isfinite(m), rng.standard_normal((S, S)).astype(np.float32)*0.5, m)
+    m[:, 3] = -np.inf               # query 3 sees nothing at all
+    return F(m.astype(np.float32))
+
+
+@pytest.mark.parametrize("head,seq,batch,group,kvh,kind", SEEDED)
+def test_fwd_bwd_against_oracle(head, seq, batch, group, kvh, kind):
+    rng = np.random.default_rng(head + seq)
+    shape = (head, seq, batch, group, kvh)
+    Q, K, V, dA = (O.to_bf16(rng.standard_normal(shape).astype(np.float32)) for _ in range(4))
+    mask = O.to_bf16(make_mask(kind, seq))
+    wantA, wantL = O.flash_forward(Q, K, V, mask)
+    A, lse, _ = run_fwd(Q, K, V, mask)
+    assert O.rel_err(bf(A), O.from_bf16(wantA)) <= BF16_TOL
+    gl = to_fortran(lse)
+    fin = np.isfinite(wantL)
+    assert np.array_equal(np.isfinite(gl), fin)
+    assert np.allclose(gl[fin], wantL[fin], rtol=1e-3, atol=1e-3)
+    if kind == "ragged":               # the fully masked row is left untouched
+        assert np.all(bf(A)[:, 3] == 0.0) and np.all(np.isneginf(gl[3]))
+    # backward from the oracle's A and lse
+    z = lambda: O.zeros(shape, np.uint16)
+    wq, wk, wv = O.flash_backward(Q, K, V, wantA, dA, mask, wantL, z(), z(), z())
+    lse_in = np.where(fin, wantL, 0.0).astype(np.float32)
+    dK, dQ, dV = (torch.zeros(tuple(reversed(shape)), dtype=torch.bfloat16, device="cuda")
+                  for _ in range(3))
+    flash_sdpa_bwd_async(dev(K), dev(Q), dev(V), dev(wantA), dev(dA), dev(mask),
+                         dev(F(lse_in)), dK, dQ, dV)
+    torch.cuda.synchronize()
+    wq2, wk2, wv2 = O.flash_backward(Q, K, V, wantA, dA, mask, F(lse_in), z(), z(), z())
+    for got, w in ((dQ, wq2), (dK, wk2), (dV, wv2)):
+        assert O.rel_err(bf(got), O.from_bf16(w)) <= BF16_TOL
+
+
+@pytest.mark.parametrize("shape,base", [
+    # tilings of tests/tensor/flash_sdpa_fwd_cudnn.cc:244-246 (head, seq, batch, group, kv)
+    ((32, 64, 1, 1, 1), (32, 64, 1, 1, 1)),
+    ((128, 256, 2, 2, 2), (128, 128, 1, 1, 1)),
+    ((32, 512, 4, 3, 4), (32, 64, 1, 1, 2)),
+    ((64, 256, 3, 4, 2), (64, 64, 3, 2, 1)),   # wrappers/python/tests/layer/test_sdpa.py:86-109
+])
+def test_tiled_equals_single_tile(shape, base):
+    rng = np.random.default_rng(42)
+    Q, K, V, dA = (O.to_bf16(rng.standard_normal(shape).astype(np.float32)*0.1)
+                   for _ in range(4))
+    S = shape[1]
+    i = np.arange(S)
+    band = F(np.where(np.abs(i[:, None] - i[None, :]) <= 32, 0.0, -np.inf).astype(np.float32))
+    mask = O.to_bf16(band)
+    A1, l1, _ = run_fwd(Q, K, V, mask)
+    A2, l2, _ = run_fwd(Q, K, V, mask, seq_tile=base[1], batch_tile=base[2:])
+    a64, l64 = O.sdpa_fp64(Q, K, V, mask)
+    assert O.rel_err(bf(A1), a64) <= 1e-2
+    assert O.rel_err(bf(A2), a64) <= 1e-2
+    assert np.allclose(to_fortran(l1), l64, rtol=1e-3, atol=1e-3)
+    assert np.allclose(to_fortran(l2), l64, rtol=1e-3, atol=1e-3)
+    q64, k64, v64 = O.sdpa_bwd_fp64(Q, K, V, to_fortran(A1), dA, mask, to_fortran(l1))
+    for tiles in (None, base):
+        dK, dQ, dV = (torch.zeros_like(A1) for _ in range(3))
+        flash_sdpa_bwd_async(dev(K), dev(Q), dev(V), A1, dev(dA), dev(mask), l1, dK, dQ, dV,
+                             None if tiles is None else base[1],
+                             None if tiles is None else base[2:])
+        torch.cuda.synchronize()
+        # many bf16 `+=` steps when tiled: the reference's own tolerance is 1e-2 per step
+        tol = 1e-2 if tiles is None else 3e-2
+        for got, w in ((dQ, q64), (dK, k64), (dV, v64)):
+            assert O.rel_err(bf(got), w) <= tol
+
+
+def test_layer_flash_forward_backward_matches_vanilla_oracle():
+    """nntile.layer.Sdpa with flash_attention=True against the unfused fp32 chain
+    of the oracle (the reference's tiled path), bf16 bar 2e-2."""
+    rng = np.random.default_rng(3)
+    shape = (64, 256, 2, 2, 2)
+    Qf, Kf, Vf, dYf = (F(rng.standard_normal(shape).astype(np.float32)) for _ in range(4))
+    Q, K, V, dY = (O.to_bf16(x) for x in (Qf, Kf, Vf, dYf))
+    maskb = F(np.triu(np.ones((256, 256), dtype=bool)))
+    q32, k32, v32, dy32 = (O.from_bf16(x) for x in (Q, K, V, dY))
+    want, attn, _ = O.vanilla_forward(q32, k32, v32, maskb)
+    wq, wk, wv = (O.zeros(shape, np.float32) for _ in range(3))
+    O.vanilla_backward(q32, k32, v32, want, dy32, attn, maskb, wq, wk, wv)
+    layer = Sdpa(dev(Q), dev(K), dev(V), mask=dev(O.to_bf16(causal_add(256))),
+                 flash_attention=True, seq_tile=128, batch_tile=(1, 2, 1))
+    y = layer.forward_async()
+    assert O.rel_err(bf(y), want) <= BF16_TOL
+    dq, dk, dv = (torch.zeros_like(layer.q) for _ in range(3))
+    layer.backward_async(dev(dY), dq, dk, dv)
+    torch.cuda.synchronize()
+    for got, w in ((dq, wq), (dk, wk), (dv, wv)):
+        assert O.rel_err(bf(got), w) <= BF16_TOL
+
+
+def test_forward_merges_into_existing_partial_result():
+    """Two K/V tiles fed by hand through the tile-level entry point: the second
+    call must merge with the (lse, A) the first one left (RW semantics)."""
+    rng = np.random.default_rng(8)
+    head, seq, batch = 64, 128, 2
+    Q, K1, V1, K2, V2 = (O.to_bf16(rng.standard_normal((head, seq, batch, 1, 1))
+                                   .astype(np.float32)) for _ in range(5))
+    zero = O.to_bf16(np.zeros((seq, seq), np.float32))
+    lse = torch.full((batch, seq), -np.inf, dtype=torch.float32, device="cuda")
+    A = torch.zeros((batch, seq, head), dtype=torch.bfloat16, device="cuda")
+    s_l = torch.empty_like(lse)
+    s_A = torch.empty_like(A)
+    for Kt, Vt in ((K1, V1), (K2, V2)):
+        ops.flash_sdpa_fwd(seq, head, batch, dev(Kt), dev(Q), dev(zero), s_l, dev(Vt), s_A,
+                           lse, A)
+    torch.cuda.synchronize()
+    Kc = np.concatenate([O.from_bf16(K1), O.from_bf16(K2)], axis=1)
+    Vc = np.concatenate([O.from_bf16(V1), O.from_bf16(V2)], axis=1)
+    a64, l64 = O.sdpa_fp64(O.from_bf16(Q), Kc, Vc, np.zeros((2*seq, seq), np.float32))
+    got = O.from_bf16(to_fortran(A.view(1, 1, batch, seq, head)))
+    assert O.rel_err(got, a64) <= 1e-2
+    assert np.allclose(lse.cpu().numpy().T, l64[:, :, 0, 0], rtol=1e-3, atol=1e-3)

@@ -158,6 +158,7 @@ def test_flash_bwd_restatement_meets_reference_test_formula(golden, seq, head, b
     Qb, Kb, Vb, Ab, dAb = (O.to_bf16(mg._as5(x, head, seq, batch)) for x in (Q, K, V, A, dA))
     mkq = O.to_bf16(F(mask.T))
     l4 = F(lse.reshape(batch, seq).T.reshape(seq, batch, 1, 1))
+    tag = f"bwd_s{seq}_h{head}_b{batch}_{'causal' if causal else 'full'}"
     zero = O.zeros(Qb.shape, np.uint16)
     z = O.flash_backward(Qb, Kb, Vb, Ab, dAb, mkq, l4, zero.copy(order="F"), zero.copy(order="F"), zero)
     for got, key in zip(z, ("_dQ", "_dK", "_dV")):
@@ -165,7 +166,6 @@ def test_flash_bwd_restatement_meets_reference_test_formula(golden, seq, head, b
     init = np.full(Qb.shape, 0.25, np.float32)
     dQ, dK, dV = (O.to_bf16(init) for _ in range(3))
     dQ, dK, dV = O.flash_backward(Qb, Kb, Vb, Ab, dAb, mkq, l4, dQ, dK, dV)
-    tag = f"bwd_s{seq}_h{head}_b{batch}_{'causal' if causal else 'full'}"
     for got, key in ((dQ, "_dQ"), (dK, "_dK"), (dV, "_dV")):
         assert O.rel_err(O.from_bf16(got), init + g[tag + key]) <= 1e-2
 
