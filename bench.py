@@ -1,0 +1,568 @@
+#!/usr/bin/env python
+"""Benchmark of the tiled SDPA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (one "step" = one forward + one backward pass of the fused
+flash-SDPA tile tasks over one batch of synthetic input, per GPU):
+  BASELINE config 3, Llama-style GQA attention, bf16 storage / fp32 accumulate:
+  32 query heads (8 KV heads x group 4, K/V replicated over the group as the
+  reference does), head_dim 128, seq 4096, batch 4, causal additive mask,
+  RoPE (base 10000) pre-applied to Q and K ~ N(0,1), dY ~ N(0,1); one sequence
+  tile (seq-tile 4096), all calls through the C ABI of include/nntile_b200.h.
+The metric is TFLOP/s under the causal convention (forward 2W, backward 5W,
+W = B*Hq*S^2*D).  Scaling is weak: every rank runs the same per-GPU workload on
+its own shard of independent (batch, kv head) units; there is no collective on
+the data path.
+
+The single JSON line also carries: `roofline` (dominant kernel = the backward
+tile task, timed live with CUDA events, against the measured sustained bf16
+GEMM rate of MEASURED_PEAKS.json), `cpu_baseline` (the reference's own CPU
+kernels timed on a bounded sample, rank 0, N=1), `e2e` (same metric through the
+same C-ABI calls with HOST buffers: pinned host -> device copies of Q, K, V, dY
+and device -> host reads of A, dQ, dK, dV inside the timed region), `clocks`
+(nvidia-smi samples taken during the timed region), `gpu_launches` (kernels of
+this library launched in the timed region, from the library's own counter) and
+`extra` (N=1 only: configs 2, 4 and the decode config 5 in GB/s vs HBM peak).
+
+`--impl reference` times the reference's CPU implementation of the path (its own
+src/kernel/*/cpu.cc + OpenBLAS sgemm, compiled in place as oracle/_ref; the C
+port of the oracle if that is absent) on all host cores, each step a bounded
+sample of the same workload, and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sdpa_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+# BASELINE config 3 (per GPU)
+C3 = dict(head=128, seq=4096, batch=4, group=4, kv_heads=8)
+C2 = dict(head=64, seq=1024, batch=8, group=1, kv_heads=12)
+C4 = dict(head=128, seq=16384, batch=1, group=1, kv_heads=16, seq_tile=2048)
+C5 = dict(head=128, max_seq=8192, batch=64, group=4, kv_heads=8)
+
+
+def causal_flops(cfg):
+    W = cfg["batch"]*cfg["group"]*cfg["kv_heads"]*cfg["seq"]**2*cfg["head"]
+    return 2.0*W, 5.0*W
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(bf16=d.get("bf16_tflops_sustained", 1400.0), bf16_burst=d.get("bf16_tflops"),
+                    hbm=d.get("hbm_gbs", 6650.0), source="measured")
+    return dict(bf16=1400.0, bf16_burst=1590.0, hbm=6650.0, source="fallback")
+
+
+# --------------------------------------------------------------------------
+# clocks sampling (nvidia-smi, during the timed region)
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.lines = []
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                pw.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = sorted(sm)[len(sm)//2:]          # upper half = samples under load
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx),
+                "power_w_max": max(pw), "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------
+# CPU reference arm (also the cpu_baseline leg)
+# --------------------------------------------------------------------------
+def cpu_reference_pass(n_slices: int, seq: int, head: int, threads: int, backend: str):
+    """Run the reference's unfused fp32 chain (forward + backward) on `n_slices`
+    independent (batch, head) slices of [head, seq], `threads` slices at a time,
+    one single-threaded BLAS per slice (the reference's own setting: tasks across
+    CPU workers, OPENBLAS_NUM_THREADS=1).  Returns seconds."""
+    import numpy as np
+
+    import oracle as O
+    rng = np.random.default_rng(2)
+    F = np.asfortranarray
+    shape = (head, seq, 1, 1, 1)
+    mask = F(np.triu(np.ones((seq, seq), dtype=bool)))
+    data = []
+    for _ in range(n_slices):
+        data.append([F(rng.standard_normal(shape).astype(np.float32)) for _ in range(4)])
+
+    def one(d):
+        Q, K, V, dY = d
+        Y, attn, _ = O.vanilla_forward(Q, K, V, mask, backend=backend)
+        dQ, dK, dV = (O.zeros(shape, np.float32) for _ in range(3))
+        O.vanilla_backward(Q, K, V, Y, dY, attn, mask, dQ, dK, dV, backend=backend)
+        return float(dQ.flat[0])
+
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(one, data))
+    return time.perf_counter() - t0
+
+
+def cpu_arm_setup():
+    import oracle as O
+    backend = "ref" if O.have_ref() else "port"
+    if backend == "ref":
+        import ctypes
+        from oracle import build as ob
+        blas = ob.find_openblas()
+        if blas:
+            try:
+                ctypes.CDLL(blas).scipy_openblas_set_num_threads(1)
+            except (OSError, AttributeError):
+                pass
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
+    return backend, max(1, int(cores))
+
+
+def cpu_sample_shape(cores: int):
+    """Bounded sample of config 3: two slices per thread at the full
+    head size and half the sequence length, so that a pass stays near a second."""
+    return dict(seq=2048, head=C3["head"], slices=2*cores)
+
+
+def run_reference_arm(args):
+    backend, cores = cpu_arm_setup()
+    smp = cpu_sample_shape(cores)
+    W = smp["slices"]*smp["seq"]**2*smp["head"]
+    flops = 7.0*W
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_pass(smp["slices"], smp["seq"], smp["head"], cores, backend)
+    times = []
+    for _ in range(args.steps):
+        times.append(cpu_reference_pass(smp["slices"], smp["seq"], smp["head"], cores, backend))
+    total = sum(times)
+    val = flops*args.steps/total/1e12
+    kind = "reference" if backend == "ref" else "port"
+    sample = (f"{smp['slices']} independent (batch, head) slices of config 3 at head "
+              f"{smp['head']}, seq {smp['seq']} (full config: seq 4096, 128 slices), fp32 "
+              f"unfused chain forward+backward, one slice per thread")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3*total/args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C3 llama-gqa attention fwd+bwd, CPU reference chain, bounded sample",
+                   "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def rope_(x, base=10000.0):
+    """Interleaved-pair RoPE over (H, G, B, S, D) in place (setup only; follows
+    wrappers/python/nntile/model/llama_attention.py:1122-1134)."""
+    import torch
+    H, G, B, S, D = x.shape
+    inv = base**(-torch.arange(0, D, 2, device=x.device, dtype=torch.float32)/D)
+    ang = torch.arange(S, device=x.device, dtype=torch.float32)[:, None]*inv[None, :]
+    cos, sin = ang.cos(), ang.sin()
+    xf = x.float()
+    a, b = xf[..., 0::2], xf[..., 1::2]
+    out = torch.empty_like(xf)
+    out[..., 0::2] = a*cos - b*sin
+    out[..., 1::2] = a*sin + b*cos
+    x.copy_(out.to(x.dtype))
+
+
+def causal_mask_tile(S, kind, device):
+    """(Sq, Sk) additive bf16 mask tile: 'diag' = -inf where k > q, 'zero', 'ninf'."""
+    import torch
+    if kind == "zero":
+        return torch.zeros((S, S), dtype=torch.bfloat16, device=device)
+    if kind == "ninf":
+        return torch.full((S, S), -math.inf, dtype=torch.bfloat16, device=device)
+    q = torch.arange(S, device=device)[:, None]
+    k = torch.arange(S, device=device)[None, :]
+    return torch.where(k > q, torch.tensor(-math.inf, device=device),
+                       torch.tensor(0.0, device=device)).to(torch.bfloat16)
+
+
+class FlashWorkload:
+    """Single-sequence-tile fused attention forward+backward through the tile-level
+    C entry points (the task the reference's tile layer submits)."""
+
+    def __init__(self, cfg, device, seed, rope=True):
+        import torch
+        from nntile_b200 import ops
+        self.ops, self.torch, self.cfg = ops, torch, cfg
+        H, G, B, S, D = cfg["kv_heads"], cfg["group"], cfg["batch"], cfg["seq"], cfg["head"]
+        g = torch.Generator(device=device).manual_seed(seed)
+        shp = (H, G, B, S, D)
+        self.q = torch.randn(shp, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        kv = torch.randn((2, H, 1, B, S, D), generator=g, device=device, dtype=torch.float32)
+        # K, V ~ N(0,1) per KV head, replicated over the group as the reference does
+        self.k = kv[0].expand(H, G, B, S, D).contiguous().to(torch.bfloat16)
+        self.v = kv[1].expand(H, G, B, S, D).contiguous().to(torch.bfloat16)
+        del kv
+        if rope:
+            rope_(self.q)
+            rope_(self.k)
+        self.dy = torch.randn(shp, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        self.mask = causal_mask_tile(S, "diag", device)
+        self.nb = H*G*B
+        self.S, self.D = S, D
+        self.y = torch.zeros(shp, dtype=torch.bfloat16, device=device)
+        self.lse = torch.empty((H, G, B, S), dtype=torch.float32, device=device)
+        self.dq, self.dk, self.dv = (torch.zeros(shp, dtype=torch.bfloat16, device=device)
+                                     for _ in range(3))
+        self.s_lse = torch.empty_like(self.lse)
+        self.s1, self.s2, self.s3 = (torch.empty(shp, dtype=torch.bfloat16, device=device)
+                                     for _ in range(3))
+        self.flops_fwd, self.flops_bwd = causal_flops(cfg)
+
+    def forward(self):
+        ops = self.ops
+        ops.fill(-math.inf, self.lse)
+        ops.clear(self.y)
+        ops.flash_sdpa_fwd(self.S, self.D, self.nb, self.k, self.q, self.mask, self.s_lse,
+                           self.v, self.s1, self.lse, self.y)
+
+    def backward(self):
+        self.ops.flash_sdpa_bwd(self.S, self.D, self.nb, self.k, self.q, self.v, self.y,
+                                self.dy, self.mask, self.lse, self.s1, self.s2, self.s3,
+                                self.dk, self.dq, self.dv)
+
+    def step(self):
+        self.forward()
+        self.backward()
+
+
+def time_steps(torch, fn, steps, warmup, barrier=None, split=None):
+    """CUDA-event timing of `steps` calls on the current stream.  `split` is an
+    optional pair of callables (fwd, bwd) timed separately inside each step."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = []
+    start.record()
+    for _ in range(steps):
+        if split:
+            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            a.record()
+            split[0]()
+            b.record()
+            split[1]()
+            c.record()
+            marks.append((a, b, c))
+        else:
+            fn()
+    stop.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    total_ms = start.elapsed_time(stop)
+    fwd_ms = [a.elapsed_time(b) for a, b, _ in marks]
+    bwd_ms = [b.elapsed_time(c) for _, b, c in marks]
+    return total_ms, fwd_ms, bwd_ms
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from nntile_b200 import _lib, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback "
+                         "(use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    peaks = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    wl = FlashWorkload(C3, dev, seed=2 + rank)
+    fwd_path = ops.flash_sdpa_path(C3["seq"], C3["head"], wl.nb)
+    bwd_path = ops.flash_sdpa_path(C3["seq"], C3["head"], wl.nb, backward=True)
+
+    for _ in range(args.warmup):
+        wl.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    n0 = lib.nntile_b200_launch_count()   # launches of the timed part only
+    total_ms, fwd_ms, bwd_ms = time_steps(torch, wl.step, args.steps, 0, barrier,
+                                          split=(wl.forward, wl.backward))
+    launches = int(lib.nntile_b200_launch_count() - n0)
+    clocks = sampler.stop()
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms/args.steps
+    flops_step = wl.flops_fwd + wl.flops_bwd
+    value = world*flops_step/(ms_per_step*1e-3)/1e12
+
+    # ---- roofline of the dominant kernel (backward tile task) -----------------
+    bwd_med = statistics.median(bwd_ms)
+    fwd_med = statistics.median(fwd_ms)
+    achieved = wl.flops_bwd/(bwd_med*1e-3)/1e12
+    roofline = {
+        "bound": "tensor", "kernel": "flash_sdpa_bwd tile task",
+        "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
+        "frac": achieved/peaks["bf16"], "peak_source": peaks["source"] + " sustained bf16 GEMM",
+        "traffic": None,
+        "fwd": {"achieved": wl.flops_fwd/(fwd_med*1e-3)/1e12, "ms": fwd_med,
+                "frac": wl.flops_fwd/(fwd_med*1e-3)/1e12/peaks["bf16"]},
+        "bwd_ms": bwd_med,
+    }
+
+    # ---- e2e: host buffers, copies inside the timed region --------------------
+    e2e_steps = max(1, min(args.steps, 5))
+    host_in = [x.cpu().pin_memory() for x in (wl.q, wl.k, wl.v, wl.dy)]
+    host_out = [torch.empty_like(x, device="cpu").pin_memory()
+                for x in (wl.y, wl.dq, wl.dk, wl.dv)]
+    dev_in = (wl.q, wl.k, wl.v, wl.dy)
+    dev_out = (wl.y, wl.dq, wl.dk, wl.dv)
+
+    def e2e_step():
+        for h, d in zip(host_in, dev_in):
+            d.copy_(h, non_blocking=True)
+        wl.step()
+        for h, d in zip(host_out, dev_out):
+            h.copy_(d, non_blocking=True)
+
+    e2e_ms, _, _ = time_steps(torch, e2e_step, e2e_steps, 1, barrier)
+    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())/e2e_steps
+    h2d = sum(x.numel()*x.element_size() for x in host_in)
+    d2h = sum(x.numel()*x.element_size() for x in host_out)
+    e2e = {"value": world*flops_step/(e2e_ms*1e-3)/1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+           "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    del host_in, host_out
+
+    extra, cpu_baseline = None, None
+    if world == 1:
+        extra = run_extras(torch, ops, lib, dev, peaks, args)
+        backend, cores = cpu_arm_setup()
+        smp = cpu_sample_shape(cores)
+        secs = cpu_reference_pass(smp["slices"], smp["seq"], smp["head"], cores, backend)
+        secs = min(secs, cpu_reference_pass(smp["slices"], smp["seq"], smp["head"], cores,
+                                            backend))
+        cpu_baseline = {
+            "value": 7.0*smp["slices"]*smp["seq"]**2*smp["head"]/secs/1e12, "unit": UNIT,
+            "cores": cores, "kind": "reference" if backend == "ref" else "port",
+            "sample": (f"{smp['slices']} slices of config 3 at head {smp['head']}, seq "
+                       f"{smp['seq']}, fp32 unfused chain fwd+bwd, one slice per thread, "
+                       f"best of 2 passes ({secs:.2f} s)")}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": "C3 llama-gqa attention fwd+bwd (BASELINE configs[2]): 32 q heads "
+                            "(8 kv x group 4), head_dim 128, seq 4096, batch 4 per GPU, causal, "
+                            "RoPE pre-applied, seq-tile 4096",
+                "per_gpu_shape": C3, "global_batch": C3["batch"]*world,
+                "flop_convention": "causal: fwd 2W, bwd 5W, W=B*Hq*S^2*D",
+                "l2": "inputs_exceed_l2 (Q,K,V,dY,A 134 MB each vs 126 MB L2)",
+                "parallelism": f"{world} independent shards of (batch, kv head) units, no collective",
+                "paths": {"fwd": fwd_path, "bwd": bwd_path,
+                          "legend": "2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel"},
+            },
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "clocks": clocks, "gpu_launches": launches, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_extras(torch, ops, lib, dev, peaks, args):
+    """Configs 2, 4 and 5 at N=1 (few steps each)."""
+    out = {}
+    steps = max(3, min(args.steps, 10))
+    # ---- config 2: GPT-2-small attention, seq-tile 1024, head-tile 12, batch-tile 8
+    wl = FlashWorkload(C2, dev, seed=1, rope=False)
+    ms, _, _ = time_steps(torch, wl.step, steps*4, 3)
+    ms /= steps*4
+    out["c2_gpt2_small_attention"] = {
+        "tflops": (wl.flops_fwd + wl.flops_bwd)/(ms*1e-3)/1e12, "ms_per_step": ms,
+        "shape": C2, "note": "one tile task per pass (batch tile 8, head tile 12); "
+                             "working set 63 MB fits L2"}
+    del wl
+    # ---- config 4: long context, seq-tile 2048, K/V tiles streamed through tasks
+    out["c4_long_context"] = run_c4(torch, ops, lib, dev, steps)
+    # ---- config 5: decode, HBM-bound
+    from nntile_b200.sdpa import decode_sdpa
+    D, L, B, G, H = C5["head"], C5["max_seq"], C5["batch"], C5["group"], C5["kv_heads"]
+    g = torch.Generator(device=dev).manual_seed(4)
+    q = torch.randn((H, G, B, 1, D), generator=g, device=dev).to(torch.bfloat16)
+    Kc = torch.randn((H, B, L, D), generator=g, device=dev).to(torch.bfloat16)
+    Vc = torch.randn((H, B, L, D), generator=g, device=dev).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    ws = torch.empty(ops.decode_workspace_bytes(D, L, B, G, H), dtype=torch.uint8, device=dev)
+    fn = lambda: decode_sdpa(q, Kc, Vc, L, out=o, workspace=ws)
+    ms, _, _ = time_steps(torch, fn, steps*4, 5)
+    ms /= steps*4
+    nbytes = 2*B*H*L*D*2 + 2*B*G*H*D*2
+    gbs = nbytes/(ms*1e-3)/1e9
+    out["c5_decode"] = {"gbs": gbs, "ms_per_step": ms, "bytes_per_step": nbytes,
+                        "frac_of_measured_hbm": gbs/peaks["hbm"], "peak_gbs": peaks["hbm"],
+                        "peak_source": peaks["source"], "shape": C5,
+                        "note": "K+V caches 2.1 GB, far above L2"}
+    return out
+
+
+def run_c4(torch, ops, lib, dev, steps):
+    """Config 4 through the tensor-level C entry points: 8 x 8 (Q tile, K/V tile)
+    tasks per pass, every pair submitted as the reference does; the mask tiles are
+    one of three buffers (zero / -inf / diagonal)."""
+    import ctypes
+    H, S, D, St = C4["kv_heads"], C4["seq"], C4["head"], C4["seq_tile"]
+    nt = S//St
+    g = torch.Generator(device=dev).manual_seed(3)
+
+    def tiles(n, fill=None):
+        if fill is None:
+            return [torch.randn((H, 1, 1, St, D), generator=g, device=dev).to(torch.bfloat16)
+                    for _ in range(n)]
+        return [torch.full((H, 1, 1, St, D), fill, dtype=torch.bfloat16, device=dev)
+                for _ in range(n)]
+
+    Q, K, V, dY = tiles(nt), tiles(nt), tiles(nt), tiles(nt)
+    A, dQ, dK, dV = tiles(nt, 0.0), tiles(nt, 0.0), tiles(nt, 0.0), tiles(nt, 0.0)
+    lse = [torch.empty((H, 1, 1, St), dtype=torch.float32, device=dev) for _ in range(nt)]
+    mz, mi, md = (causal_mask_tile(St, k, dev) for k in ("zero", "ninf", "diag"))
+    masks = []
+    for qi in range(nt):            # tile (k, q) stored at k + q*nt
+        for ki in range(nt):
+            masks.append(mz if ki < qi else md if ki == qi else mi)
+
+    def parr(ts):
+        return ctypes.cast((ctypes.c_void_p*len(ts))(*[t.data_ptr() for t in ts]),
+                           ctypes.POINTER(ctypes.c_void_p))
+
+    i64 = ctypes.c_int64
+    shape = (i64*5)(D, S, 1, 1, H)
+    base = (i64*5)(D, St, 1, 1, H)
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(base)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    pk = {n: parr(t) for n, t in dict(Q=Q, K=K, V=V, dY=dY, A=A, dQ=dQ, dK=dK, dV=dV, lse=lse,
+                                      m=masks).items()}
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def step():
+        for t in lse:
+            ops.fill(-math.inf, t)
+        for t in A:
+            ops.clear(t)
+        st = lib.nntile_b200_tensor_flash_sdpa_fwd_bf16(
+            stream(), shape, base, pk["K"], pk["Q"], pk["m"], pk["lse"], pk["V"], pk["A"],
+            ctypes.c_void_p(scratch.data_ptr()), nbytes)
+        assert st == 0, st
+        st = lib.nntile_b200_tensor_flash_sdpa_bwd_bf16(
+            stream(), shape, base, pk["K"], pk["Q"], pk["V"], pk["A"], pk["dY"], pk["m"],
+            pk["lse"], pk["dK"], pk["dQ"], pk["dV"], ctypes.c_void_p(scratch.data_ptr()), nbytes)
+        assert st == 0, st
+
+    ms, _, _ = time_steps(torch, step, steps, 2)
+    ms /= steps
+    f, b = causal_flops(dict(batch=1, group=1, kv_heads=H, seq=S, head=D))
+    return {"tflops": (f + b)/(ms*1e-3)/1e12, "ms_per_step": ms, "shape": C4,
+            "tasks_per_pass": nt*nt,
+            "note": "all 64 tile pairs submitted per pass (28 fully masked), causal-convention flops"}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    args = ap.parse_args(argv)
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return 0                 # rank 0 alone runs the CPU arm
+        run_reference_arm(args)
+        return 0
+    run_gpu_arm(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
