@@ -1,6 +1,638 @@
+// Fused flash-SDPA forward tile task for B200: tcgen05 MMA with TMEM
+// accumulators, Q/K/V staged by TMA, online max / sum-exp in registers, and the
+// log-sum-exp merge into the running (lse, A) fused into the epilogue.
+//
+// Replaces, for head in {64, 128} and seq a multiple of 128, what
+// src/kernel/flash_sdpa_fwd_cudnn/cuda.cc:145-202 does with a cuDNN graph, a
+// scratch copy of the tile result and accumulate_attn_output
+// (src/kernel/accumulate_attn_output/cuda.cu:28-113).
+//
+// Work decomposition.  One CTA owns two 128-row query tiles of one batch entry
+// (one (batch, head) slice) and walks the 128-key blocks that at least one of
+// them needs.  384 threads (three warpgroups) in three roles; the control
+// warpgroup hands most of its registers to the softmax warpgroups (setmaxnreg):
+//   warp 0      TMA producer: Q tiles once, then K and V blocks through two
+//               2-stage rings (64-column panels, 128-byte swizzle)
+//   warp 1      MMA issuer: S_t = Q_t K^T (operands in shared memory) and
+//               O_t += P_t V (P_t read from TMEM, V MN-major from shared memory);
+//               owns the TMEM allocation (512 columns: S_0 S_1 O_0 O_1)
+//   warps 4-11  two softmax groups of 128 threads, one per query tile, one thread
+//               per query row: tcgen05.ld of the S row, bias, running max with a
+//               lazy rescale of O (only when the max grows by more than 2^8),
+//               exp2, bf16 P written back into the S columns, and at the end the
+//               normalisation, the merge with the stored (lse, A) and the store.
+// While one group is busy with exponentials the tensor pipe works for the other
+// tile (PV_0, QK_0', PV_1, QK_1' ...), so MUFU and MMA overlap.
+//
+// The additive mask is a general bias in the reference.  A small pre-pass
+// classifies every 128x128 block of it as all-zero, all -inf, exact causal
+// diagonal or generic; -inf blocks are never loaded or multiplied, zero blocks
+// never read the mask, diagonal blocks compare indices, generic blocks add the
+// bias from global memory.  The class table lives in the scratch buffer the
+// reference's tile layer provides to every task, so nothing is allocated here.
+//
+// Every mbarrier wait is bounded (sm100.cuh); a wait that gives up sets a status
+// word at the start of the scratch buffer and the CTA tears down normally.
 #include "flash.cuh"
+#include "sm100.cuh"
+
 namespace nb200 {
-bool flash_fwd_sm100_supports(Index, Index, Index) { return false; }
-int flash_fwd_sm100(cudaStream_t, Index, Index, Index, const bf16 *, const bf16 *, const bf16 *,
-        const bf16 *, float *, bf16 *, void *, size_t) { return NNTILE_B200_E_SHAPE; }
+
+using namespace sm100;
+
+namespace fwd {
+
+constexpr int BLK = 128;             // query rows per tile and keys per block
+constexpr int THREADS = 384;         // 3 warpgroups: control, softmax 0, softmax 1
+constexpr int KV_STAGES = 2;
+constexpr int MAX_BLOCKS = 512;      // seq <= 65536
+constexpr float LOG2E_F = 1.4426950408889634f;
+constexpr float LN2_F = 0.6931471805599453f;
+constexpr float RESCALE_STEP = 8.0f;
+enum : uint8_t { CLS_ZERO = 0, CLS_SKIP = 1, CLS_GENERIC = 2, CLS_CAUSAL = 3 };
+constexpr size_t CLS_OFFSET = 256;   // class table offset inside the scratch buffer
+
+// ------------------------------------------------------------ mask classifier
+// grid (key block, query block), 256 threads; also clears the status word.
+__global__ void __launch_bounds__(256)
+mask_classify_kernel(int seq, int nblk, const bf16 *__restrict__ mask, uint8_t *scratch)
+{
+    const int kb = blockIdx.x, qb = blockIdx.y;
+    int zero = 1, ninf = 1, causal = 1;
+#pragma unroll
+    for(int i = 0; i < 8; ++i)
+    {
+        const int u = threadIdx.x + 256*i;
+        const int row = u >> 4, c16 = u & 15;
+        const uint4 v = *reinterpret_cast<const uint4 *>(
+                mask + (size_t)(qb*BLK + row)*seq + kb*BLK + c16*8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for(int e = 0; e < 8; ++e)
+        {
+            const uint32_t bits = (w[e >> 1] >> (16*(e & 1))) & 0xFFFFu;
+            const bool is_zero = (bits & 0x7FFFu) == 0u, is_ninf = bits == 0xFF80u;
+            zero &= is_zero;
+            ninf &= is_ninf;
+            causal &= (c16*8 + e > row) ? is_ninf : is_zero;
+        }
+    }
+    zero = __syncthreads_and(zero);
+    ninf = __syncthreads_and(ninf);
+    causal = __syncthreads_and(causal);
+    if(threadIdx.x == 0)
+    {
+        scratch[CLS_OFFSET + (size_t)qb*nblk + kb] =
+                zero ? CLS_ZERO : ninf ? CLS_SKIP : causal ? CLS_CAUSAL : CLS_GENERIC;
+        if(kb == 0 && qb == 0)
+        {
+            *reinterpret_cast<uint32_t *>(scratch) = 0u;
+        }
+    }
 }
+
+// ------------------------------------------------------------- shared storage
+template<int D>
+struct Smem
+{
+    static constexpr int TILE_BYTES = BLK*D*2;
+    uint8_t q[2][TILE_BYTES];
+    uint8_t k[KV_STAGES][TILE_BYTES];
+    uint8_t v[KV_STAGES][TILE_BYTES];
+    uint64_t q_full[2];
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+    uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+    uint64_t s_full[2], p_full[2], o_full[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+    int nproc;
+    int nact[2];
+    uint16_t list[MAX_BLOCKS];       // key blocks to walk, in order
+    uint8_t cls[2][MAX_BLOCKS];      // class of list[it] for tile 0 / tile 1
+};
+
+template<int D>
+__device__ __forceinline__ void load_tile(uint8_t *dst, const CUtensorMap *map, uint64_t *bar,
+        int row)
+{
+#pragma unroll
+    for(int p = 0; p < D/64; ++p)
+    {
+        tma_load_2d(dst + p*(BLK*128), map, bar, 64*p, row);
+    }
+}
+
+// S_t = Q_t K^T: D/16 k-steps, both operands K-major, 64-column panels.
+template<int D>
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, const uint8_t *q, const uint8_t *k)
+{
+    constexpr uint32_t idesc = idesc_bf16(BLK, BLK, 0, 0);
+    const uint32_t qa = smem_u32(q), ka = smem_u32(k);
+#pragma unroll
+    for(int ks = 0; ks < D/16; ++ks)
+    {
+        const uint32_t off = (ks >> 2)*(BLK*128) + (ks & 3)*32;
+        mma_ss(d_tmem, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
+                idesc, ks > 0);
+    }
+}
+
+// O_t (+)= P_t V: 8 k-steps of 16 keys; P from TMEM (8 columns per step), V
+// MN-major: 16 key rows = 2048 bytes per step, next 64 head columns 16 KB away.
+template<int D>
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, const uint8_t *v,
+        bool accumulate)
+{
+    constexpr uint32_t idesc = idesc_bf16(BLK, D, 0, 1);
+    const uint32_t va = smem_u32(v);
+#pragma unroll
+    for(int ks = 0; ks < BLK/16; ++ks)
+    {
+        mma_ts(d_tmem, p_tmem + 8*ks, smem_desc_sw128(va + ks*2048, BLK*128, 1024), idesc,
+                (accumulate || ks > 0) ? 1u : 0u);
+    }
+}
+
+template<int D>
+__global__ void __launch_bounds__(THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
+        const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+        int seq, int batch, float scale_log2, const bf16 *__restrict__ mask,
+        uint8_t *scratch, float *__restrict__ lse, bf16 *__restrict__ A)
+{
+    extern __shared__ uint8_t smem_raw[];
+    Smem<D> &sm = *reinterpret_cast<Smem<D> *>(
+            (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nblk = seq/BLK;
+    const int npairs = (nblk + 1)/2;
+    const int pair = npairs - 1 - (int)(blockIdx.x/batch);     // heavy (late) rows first
+    const int b = (int)(blockIdx.x % batch);
+    const int qb0 = 2*pair, qb1 = 2*pair + 1;
+    const bool has1 = qb1 < nblk;
+    const uint8_t *cls_tab = scratch + CLS_OFFSET;
+    volatile uint32_t *abort_flag = &sm.abort_flag;
+
+    // ---- set-up: barriers, TMEM, list of key blocks ---------------------------
+    if(tid == 0)
+    {
+        for(int i = 0; i < 2; ++i)
+        {
+            mbar_init(&sm.q_full[i], 1);
+            mbar_init(&sm.s_full[i], 1);
+            mbar_init(&sm.p_full[i], 128);
+            mbar_init(&sm.o_full[i], 1);
+        }
+        for(int i = 0; i < KV_STAGES; ++i)
+        {
+            mbar_init(&sm.k_full[i], 1);
+            mbar_init(&sm.k_empty[i], 1);
+            mbar_init(&sm.v_full[i], 1);
+            mbar_init(&sm.v_empty[i], 1);
+        }
+        // a CTA of this launch that gave up earlier tells the others to skip their work
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(scratch) != 0u ? 1u : 0u;
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+    }
+    if(warp == 1)
+    {
+        tmem_alloc(&sm.tmem_base, 512);
+    }
+    if(warp == 0)
+    {
+        // compact the key blocks at least one tile needs (ballot compaction)
+        int count = 0, n0 = 0, n1 = 0;
+        for(int base = 0; base < nblk; base += 32)
+        {
+            const int kb = base + lane;
+            uint8_t c0 = CLS_SKIP, c1 = CLS_SKIP;
+            if(kb < nblk)
+            {
+                c0 = cls_tab[(size_t)qb0*nblk + kb];
+                c1 = has1 ? cls_tab[(size_t)qb1*nblk + kb] : (uint8_t)CLS_SKIP;
+            }
+            const bool need = c0 != CLS_SKIP || c1 != CLS_SKIP;
+            const uint32_t m = __ballot_sync(0xffffffffu, need);
+            if(need)
+            {
+                const int pos = count + __popc(m & ((1u << lane) - 1u));
+                sm.list[pos] = (uint16_t)kb;
+                sm.cls[0][pos] = c0;
+                sm.cls[1][pos] = c1;
+            }
+            count += __popc(m);
+            n0 += __popc(__ballot_sync(0xffffffffu, c0 != CLS_SKIP));
+            n1 += __popc(__ballot_sync(0xffffffffu, c1 != CLS_SKIP));
+        }
+        if(lane == 0)
+        {
+            sm.nproc = count;
+            sm.nact[0] = n0;
+            sm.nact[1] = n1;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const int nproc = sm.abort_flag != 0u ? 0 : sm.nproc;
+    constexpr uint32_t TILE_BYTES = Smem<D>::TILE_BYTES;
+    const int row_base = b*seq;                   // first row of this batch entry
+
+    if(warp < 4)
+    {
+    // control warpgroup: give registers away, then producer / MMA issuer / idle
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    if(warp == 0)
+    {
+        // =============================== TMA producer ==========================
+        if(lane == 0 && nproc > 0)
+        {
+            bool ok = true;
+            if(sm.nact[0] > 0)
+            {
+                mbar_arrive_expect_tx(&sm.q_full[0], TILE_BYTES);
+                load_tile<D>(sm.q[0], &tmap_q, &sm.q_full[0], row_base + qb0*BLK);
+            }
+            if(sm.nact[1] > 0)
+            {
+                mbar_arrive_expect_tx(&sm.q_full[1], TILE_BYTES);
+                load_tile<D>(sm.q[1], &tmap_q, &sm.q_full[1], row_base + qb1*BLK);
+            }
+            for(int it = 0; it < nproc && ok; ++it)
+            {
+                const int st = it % KV_STAGES;
+                const uint32_t ph = (uint32_t)(it/KV_STAGES) & 1u;
+                const int krow = row_base + (int)sm.list[it]*BLK;
+                ok = mbar_wait(&sm.k_empty[st], ph ^ 1u, abort_flag);
+                if(!ok) break;
+                mbar_arrive_expect_tx(&sm.k_full[st], TILE_BYTES);
+                load_tile<D>(sm.k[st], &tmap_k, &sm.k_full[st], krow);
+                ok = mbar_wait(&sm.v_empty[st], ph ^ 1u, abort_flag);
+                if(!ok) break;
+                mbar_arrive_expect_tx(&sm.v_full[st], TILE_BYTES);
+                load_tile<D>(sm.v[st], &tmap_v, &sm.v_full[st], krow);
+            }
+            if(!ok)
+            {
+                atomicExch(reinterpret_cast<uint32_t *>(scratch), 1u);
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ================================ MMA issuer ===========================
+        if(lane == 0 && nproc > 0)
+        {
+            bool ok = true;
+            const uint32_t s_tm[2] = {tmem, tmem + 128};
+            const uint32_t o_tm[2] = {tmem + 256, tmem + 256 + D};
+            int qk_done[2] = {-1, -1};          // last iteration whose QK_t was issued
+            int n_pv[2] = {0, 0};               // PV steps issued per tile
+            int k_waited = -1, k_released = -1;
+            uint32_t p_phase[2] = {0, 0};
+            for(int t = 0; t < 2 && ok; ++t)
+            {
+                if(sm.nact[t] > 0)
+                {
+                    ok = mbar_wait(&sm.q_full[t], 0, abort_flag);
+                }
+            }
+            auto qk = [&](int t, int it) -> bool
+            {
+                const int st = it % KV_STAGES;
+                if(it > k_waited)
+                {
+                    if(!mbar_wait(&sm.k_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag))
+                    {
+                        return false;
+                    }
+                    k_waited = it;
+                    tc_fence_after_sync();
+                }
+                issue_qk<D>(s_tm[t], sm.q[t], sm.k[st]);
+                tc_commit(&sm.s_full[t]);
+                qk_done[t] = it;
+                // release the K stage once every tile that needs this block has issued
+                const int o = t ^ 1;
+                if(it > k_released && (sm.cls[o][it] == CLS_SKIP || qk_done[o] >= it))
+                {
+                    tc_commit(&sm.k_empty[st]);
+                    k_released = it;
+                }
+                return true;
+            };
+            for(int it = 0; it < nproc && ok; ++it)
+            {
+                const int st = it % KV_STAGES;
+                for(int t = 0; t < 2 && ok; ++t)
+                {
+                    if(sm.cls[t][it] != CLS_SKIP && qk_done[t] < it)
+                    {
+                        ok = qk(t, it);
+                    }
+                }
+                if(!ok) break;
+                ok = mbar_wait(&sm.v_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag);
+                const int last_t = sm.cls[1][it] != CLS_SKIP ? 1 : 0;
+                for(int t = 0; t < 2 && ok; ++t)
+                {
+                    if(sm.cls[t][it] == CLS_SKIP)
+                    {
+                        continue;
+                    }
+                    ok = mbar_wait(&sm.p_full[t], p_phase[t], abort_flag);
+                    if(!ok) break;
+                    p_phase[t] ^= 1u;
+                    tc_fence_after_sync();
+                    issue_pv<D>(o_tm[t], s_tm[t], sm.v[st], n_pv[t] > 0);
+                    ++n_pv[t];
+                    if(t == last_t)
+                    {
+                        tc_commit(&sm.v_empty[st]);
+                    }
+                    if(n_pv[t] == sm.nact[t])
+                    {
+                        tc_commit(&sm.o_full[t]);
+                    }
+                    else if(it + 1 < nproc && sm.cls[t][it + 1] != CLS_SKIP)
+                    {
+                        ok = qk(t, it + 1);
+                    }
+                }
+            }
+            if(!ok)
+            {
+                atomicExch(reinterpret_cast<uint32_t *>(scratch), 2u);
+            }
+        }
+    }
+    }
+    else
+    {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        // ============================= softmax groups ==========================
+        const int t = (warp - 4) >> 2;                    // query tile of this group
+        const int r = 32*(warp & 3) + lane;               // row inside the tile
+        const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
+        const uint32_t s_tm = tmem + 128*t + lane_sel;
+        const uint32_t o_tm = tmem + 256 + D*t + lane_sel;
+        const int qb = t == 0 ? qb0 : qb1;
+        const int nact = sm.nact[t];
+        float m_used = -CUDART_INF_F, l = 0.0f;
+        int n = 0;
+        bool ok = true;
+        uint32_t s_phase = 0;
+        for(int it = 0; it < nproc && ok && n < nact; ++it)
+        {
+            const uint8_t c = sm.cls[t][it];
+            if(c == CLS_SKIP)
+            {
+                continue;
+            }
+            ok = mbar_wait(&sm.s_full[t], s_phase, abort_flag);
+            if(!ok) break;
+            s_phase ^= 1u;
+            tc_fence_after_sync();
+            uint32_t s[4][32];
+            tmem_ld32(s_tm, s[0]);
+            tmem_ld32(s_tm + 32, s[1]);
+            tmem_ld32(s_tm + 64, s[2]);
+            tmem_ld32(s_tm + 96, s[3]);
+            tmem_ld_wait();
+            // ---- bias; x = s*scale_log2 + bias*log2e is formed lazily below ------
+            float top_raw = -CUDART_INF_F;
+            if(c == CLS_GENERIC)
+            {
+                const bf16 *mrow = mask + (size_t)(qb*BLK + r)*seq + (size_t)sm.list[it]*BLK;
+#pragma unroll
+                for(int g = 0; g < 16; ++g)
+                {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(mrow + 8*g);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for(int e = 0; e < 8; ++e)
+                    {
+                        const float bias = __uint_as_float(
+                                (e & 1) ? (w[e >> 1] & 0xFFFF0000u) : (w[e >> 1] << 16));
+                        const float x = fmaf(__uint_as_float(s[g >> 2][8*(g & 3) + e]), scale_log2,
+                                bias*LOG2E_F);
+                        s[g >> 2][8*(g & 3) + e] = __float_as_uint(x);
+                        top_raw = fmaxf(top_raw, x);
+                    }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for(int j = 0; j < 128; ++j)
+                {
+                    if(c == CLS_CAUSAL && j > r)
+                    {
+                        s[j >> 5][j & 31] = __float_as_uint(-CUDART_INF_F);
+                    }
+                    top_raw = fmaxf(top_raw, __uint_as_float(s[j >> 5][j & 31]));
+                }
+            }
+            const float mul = c == CLS_GENERIC ? 1.0f : scale_log2;
+            const float m_blk = top_raw*mul;               // -inf stays -inf
+            // ---- lazy rescale ----------------------------------------------------
+            const bool grow = m_blk > m_used + RESCALE_STEP;   // true on the first finite block
+            const float m_new = grow ? m_blk : m_used;
+            const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
+            if(n > 0 && __any_sync(0xffffffffu, grow))
+            {
+#pragma unroll
+                for(int cc = 0; cc < D/32; ++cc)
+                {
+                    uint32_t o[32];
+                    tmem_ld32(o_tm + 32*cc, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int j = 0; j < 32; ++j)
+                    {
+                        o[j] = __float_as_uint(__uint_as_float(o[j])*alpha);
+                    }
+                    tmem_st32(o_tm + 32*cc, o);
+                }
+                tmem_st_wait();
+            }
+            l *= alpha;
+            m_used = m_new;
+            const float neg_ref = m_used == -CUDART_INF_F ? 0.0f : -m_used;
+            // ---- P = exp2(x - m), row sum, bf16 pack, back into the S columns -----
+            float part = 0.0f;
+#pragma unroll
+            for(int h = 0; h < 2; ++h)
+            {
+                uint32_t pk[32];
+#pragma unroll
+                for(int j = 0; j < 32; ++j)
+                {
+                    const float p0 = ex2(fmaf(__uint_as_float(s[2*h + (j >> 4)][(2*j) & 31]), mul, neg_ref));
+                    const float p1 = ex2(fmaf(__uint_as_float(s[2*h + (j >> 4)][(2*j + 1) & 31]), mul, neg_ref));
+                    part += p0 + p1;
+                    pk[j] = pack_bf16x2(p0, p1);
+                }
+                tmem_st32(s_tm + 32*h, pk);
+            }
+            l += part;
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_full[t]);
+            ++n;
+        }
+        // ---- epilogue: normalise, merge with the stored (lse, A), store ---------
+        if(ok && nact > 0)
+        {
+            ok = mbar_wait(&sm.o_full[t], 0, abort_flag);
+        }
+        if(ok && nact > 0)
+        {
+            tc_fence_after_sync();
+            const size_t R = (size_t)row_base + (size_t)qb*BLK + r;
+            const float in = l > 0.0f ? (m_used + log2f(l))*LN2_F : -CUDART_INF_F;
+            // rows with nothing to add stay untouched; the TMEM loads below are
+            // warp-collective, so only the global accesses are predicated
+            const bool live = isfinite(in);
+            float w_dst = 0.0f, w_src = 0.0f;
+            if(live)
+            {
+                const float old = lse[R];
+                float e, big;
+                if(old > in)
+                {
+                    big = old;
+                    e = expf(in - big);
+                    w_dst = 1.0f/(1.0f + e);
+                    w_src = e*w_dst;
+                }
+                else
+                {
+                    big = in;
+                    e = expf(old - big);
+                    w_src = 1.0f/(1.0f + e);
+                    w_dst = e*w_src;
+                }
+                lse[R] = big + logf(1.0f + e);
+            }
+            const float inv = live ? 1.0f/l : 0.0f;
+            uint4 *arow = reinterpret_cast<uint4 *>(A + R*D);
+#pragma unroll
+            for(int cc = 0; cc < D/32; ++cc)
+            {
+                uint32_t o[32];
+                tmem_ld32(o_tm + 32*cc, o);
+                tmem_ld_wait();
+                if(live)
+                {
+#pragma unroll
+                    for(int g = 0; g < 4; ++g)
+                    {
+                        uint4 prev = make_uint4(0u, 0u, 0u, 0u);
+                        if(w_dst != 0.0f)      // a weight of zero never reads the old row
+                        {
+                            prev = arow[4*cc + g];
+                        }
+                        const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
+                        uint32_t outw[4];
+#pragma unroll
+                        for(int e2 = 0; e2 < 4; ++e2)
+                        {
+                            // the tile result is rounded to storage before the merge,
+                            // as the reference's scratch output is
+                            const float a0 = __bfloat162float(__float2bfloat16_rn(
+                                    __uint_as_float(o[8*g + 2*e2])*inv));
+                            const float a1 = __bfloat162float(__float2bfloat16_rn(
+                                    __uint_as_float(o[8*g + 2*e2 + 1])*inv));
+                            const float p0 = __uint_as_float(pw[e2] << 16);
+                            const float p1 = __uint_as_float(pw[e2] & 0xFFFF0000u);
+                            outw[e2] = pack_bf16x2(w_dst*p0 + w_src*a0, w_dst*p1 + w_src*a1);
+                        }
+                        arow[4*cc + g] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                    }
+                }
+            }
+        }
+        if(!ok && lane == 0)
+        {
+            atomicExch(reinterpret_cast<uint32_t *>(scratch), 3u);
+        }
+    }
+    // ---- tear-down ---------------------------------------------------------------
+    if(*abort_flag != 0u && tid == 0)
+    {
+        // give copies still in flight time to land before the CTA's memory goes away
+        for(int i = 0; i < 64; ++i)
+        {
+            __nanosleep(1000);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if(warp == 1)
+    {
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+} // namespace fwd
+
+bool flash_fwd_sm100_supports(Index seq, Index head, Index batch)
+{
+    return (head == 64 || head == 128) && seq >= fwd::BLK && seq % fwd::BLK == 0
+            && seq/fwd::BLK <= fwd::MAX_BLOCKS && batch >= 1
+            && batch*seq < ((Index)1 << 31) && batch*((seq/fwd::BLK + 1)/2) < ((Index)1 << 31);
+}
+
+template<int D>
+static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const bf16 *Q,
+        const bf16 *mask, const bf16 *V, float *lse, bf16 *A, uint8_t *scratch)
+{
+    using namespace fwd;
+    CUtensorMap tq, tk, tv;
+    const uint64_t rows = (uint64_t)batch*seq;
+    if(!make_tmap_bf16_sw128(&tq, Q, rows, D, BLK) || !make_tmap_bf16_sw128(&tk, K, rows, D, BLK)
+            || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK))
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    const int nblk = (int)(seq/BLK);
+    mask_classify_kernel<<<dim3(nblk, nblk), 256, 0, s>>>((int)seq, nblk, mask, scratch);
+    if(launch_status() != NNTILE_B200_OK)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    static const size_t smem_bytes = sizeof(Smem<D>) + 1024;
+    static const cudaError_t attr = cudaFuncSetAttribute(flash_fwd_kernel<D>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    if(attr != cudaSuccess)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    const unsigned grid = (unsigned)(((nblk + 1)/2)*batch);
+    const float scale_log2 = LOG2E_F/sqrtf((float)D);
+    flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, (int)seq, (int)batch,
+            scale_log2, mask, scratch, lse, A);
+    return launch_status();
+}
+
+int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
+        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A, void *scratch,
+        size_t scratch_bytes)
+{
+    const size_t nblk = (size_t)(seq/fwd::BLK);
+    if(scratch_bytes < fwd::CLS_OFFSET + nblk*nblk)
+    {
+        return NNTILE_B200_E_SCRATCH;
+    }
+    uint8_t *sc = static_cast<uint8_t *>(scratch);
+    return head == 128
+            ? fwd_run<128>(s, seq, batch, K, Q, mask, V, lse, A, sc)
+            : fwd_run<64>(s, seq, batch, K, Q, mask, V, lse, A, sc);
+}
+
+} // namespace nb200

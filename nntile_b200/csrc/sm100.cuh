@@ -65,28 +65,47 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return done != 0;
 }
 
-// Every wait in these kernels is bounded: after `limit` polls, or as soon as a
-// sibling role has given up (`*abort_flag` set), the wait returns false; the
-// caller records where it stopped and leaves its loop, and the CTA tears down
-// normally.  A wait never spins forever and never traps.
-constexpr uint32_t WAIT_LIMIT = 20u*1000u*1000u;
+// Every wait in these kernels is bounded: it gives up after WAIT_LIMIT_NS of
+// wall time, or as soon as a sibling role has given up (`*abort_flag` set), and
+// returns false; the caller records where it stopped and leaves its loop, and
+// the CTA tears down normally.  A wait never spins forever and never traps.
+constexpr uint64_t WAIT_LIMIT_NS = 200ull*1000ull*1000ull;
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
         volatile uint32_t *abort_flag)
 {
-    for(uint32_t spin = 0; spin < WAIT_LIMIT; ++spin)
+    if(mbar_try_wait(bar, parity))
     {
-        if(mbar_try_wait(bar, parity))
+        return true;
+    }
+    const uint64_t t0 = global_timer_ns();
+    for(;;)
+    {
+#pragma unroll 1
+        for(int spin = 0; spin < 128; ++spin)
         {
-            return true;
+            if(mbar_try_wait(bar, parity))
+            {
+                return true;
+            }
         }
-        if((spin & 1023u) == 1023u && *abort_flag != 0u)
+        if(*abort_flag != 0u)
         {
             return false;
         }
+        if(global_timer_ns() - t0 > WAIT_LIMIT_NS)
+        {
+            *abort_flag = 1u;
+            return false;
+        }
     }
-    *abort_flag = 1u;
-    return false;
 }
 
 // ------------------------------------------------------------------------ TMA

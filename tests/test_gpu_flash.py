@@ -221,6 +221,10 @@ def test_forward_merges_into_existing_partial_result():
         ops.flash_sdpa_fwd(seq, head, batch, dev(Kt), dev(Q), dev(zero), s_l, dev(Vt), s_A,
                            lse, A)
     torch.cuda.synchronize()
+    if ops.flash_sdpa_path(seq, head, batch) == 2:
+        # status word of the tcgen05 kernel at the start of the scratch buffer:
+        # 0 = every bounded wait completed
+        assert int(s_A.view(torch.int32).flatten()[0].item()) == 0
     Kc = np.concatenate([O.from_bf16(K1), O.from_bf16(K2)], axis=1)
     Vc = np.concatenate([O.from_bf16(V1), O.from_bf16(V2)], axis=1)
     a64, l64 = O.sdpa_fp64(O.from_bf16(Q), Kc, Vc, np.zeros((2*seq, seq), np.float32))
