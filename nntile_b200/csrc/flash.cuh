@@ -26,4 +26,22 @@ int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf
         const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV,
         bf16 *dK, bf16 *dQ, bf16 *dV);
 
+// Classes of a 128x128 block of the additive mask [seq_q][seq_k].
+enum : uint8_t
+{
+    CLS_ZERO = 0,     // every entry 0: the mask is not read
+    CLS_SKIP = 1,     // every entry -inf: the block is never loaded or multiplied
+    CLS_GENERIC = 2,  // anything else: the bias is read from global memory
+    CLS_CAUSAL = 3    // exactly 0 where key <= query and -inf above the diagonal
+};
+
+// Layout of the scratch buffer the tcgen05 kernels use: a 32-bit status word at
+// offset 0 (0 = every bounded wait completed), the class table
+// [query block][key block] at CLS_OFFSET.
+constexpr size_t CLS_OFFSET = 256;
+
+// Classify every block of `mask` into scratch + CLS_OFFSET and clear the status
+// word (flash_fwd_sm100.cu).
+int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *scratch);
+
 } // namespace nb200

@@ -1,7 +1,643 @@
+// Fused flash-SDPA backward tile task for B200: five tcgen05 MMAs per
+// (query block, key block) pair with TMEM accumulators, tiles staged by TMA.
+//
+// Replaces, for head in {64, 128} and seq a multiple of 128, what
+// src/kernel/flash_sdpa_bwd_cudnn/cuda.cc:171-218 does with a cuDNN backward
+// graph into scratch followed by three add_inplace passes: gradients of one
+// (Q tile, K/V tile) task from the GIVEN A and lse, rounded to bf16 and ADDED
+// into dK, dQ, dV.
+//
+// One CTA owns one block of 128 keys of one batch entry: K and V stay in shared
+// memory, dK and dV stay in TMEM for the whole loop over the query blocks that
+// see these keys.  Everything is computed transposed (rows = keys) so that the
+// probabilities land in TMEM exactly where the next MMA wants its A operand:
+//   S^T  = K Q^T          (shared x shared, both K-major)
+//   dP^T = V dO^T         (shared x shared)
+//   P^T  = exp2(S^T*c - lse2), dS^T = P^T o (dP^T - delta)      softmax warps
+//   dV  += P^T dO         (P^T from TMEM, dO MN-major from shared memory)
+//   dK  += dS^T Q         (dS^T from TMEM, Q MN-major)
+//   dQ_i = dS K           (dS^T written to shared memory by the softmax warps,
+//                          read as an MN-major A operand; K MN-major)
+// dQ_i is added into an fp32 accumulator in global memory with vector red.add
+// (several key blocks contribute to a query row), converted and added into dQ by
+// a small epilogue kernel.  TMEM: S^T 128 + dP^T 128 + dV D + dK D columns; for
+// head 128 that is all 512, so dQ_i reuses the dP^T columns once dK has consumed
+// dS^T (the MMA pipe runs in issue order) and the next dP^T waits for the drain.
+//
+// 512 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 dQ drain,
+// warps 8-15 softmax (two warps per TMEM lane quarter, 64 query columns each).
+//
+// The fp32 dQ accumulator, delta = rowsum(A o dA), lse*log2(e) and the mask
+// class table live in the three scratch buffers the reference's tile layer
+// hands to every task (they only ever held cuDNN's scratch gradients), so the
+// library allocates nothing.  All waits are bounded (sm100.cuh).
 #include "flash.cuh"
+#include "sm100.cuh"
+
 namespace nb200 {
-bool flash_bwd_sm100_supports(Index, Index, Index) { return false; }
-int flash_bwd_sm100(cudaStream_t, Index, Index, Index, const bf16 *, const bf16 *, const bf16 *,
-        const bf16 *, const bf16 *, const bf16 *, const float *, void *, void *, void *,
-        bf16 *, bf16 *, bf16 *) { return NNTILE_B200_E_SHAPE; }
+
+using namespace sm100;
+
+namespace bwd {
+
+constexpr int BLK = 128;
+constexpr int THREADS = 512;
+constexpr int MAX_BLOCKS = 256;      // seq <= 32768
+constexpr float LOG2E_F = 1.4426950408889634f;
+
+template<int D>
+struct Smem
+{
+    static constexpr int TILE_BYTES = BLK*D*2;
+    uint8_t k[TILE_BYTES];
+    uint8_t v[TILE_BYTES];
+    uint8_t q[2][TILE_BYTES];
+    uint8_t g[2][TILE_BYTES];            // dO
+    uint8_t ds[BLK*BLK*2];               // dS^T, [key rows][query cols], swizzled
+    float stats[2][BLK];                 // [0] lse*log2e, [1] delta of the query block
+    uint64_t kv_full;
+    uint64_t q_full[2], q_empty[2], g_full[2], g_empty[2];
+    uint64_t s_full, dp_full, pds_full, dq_full, dq_empty, acc_full;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+    int nact;
+    uint8_t cls[MAX_BLOCKS];             // class of (query block qb, this key block)
+};
+
+// delta[r] = sum_h A[r,h]*dA[r,h];  lse2[r] = lse[r]*log2(e)
+__global__ void bwd_prep_kernel(int head, Index rows, const bf16 *__restrict__ A,
+        const bf16 *__restrict__ dA, const float *__restrict__ lse,
+        float *__restrict__ delta, float *__restrict__ lse2)
+{
+    const int lane = threadIdx.x & 31;
+    const Index r = (Index)blockIdx.x*(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if(r >= rows)
+    {
+        return;
+    }
+    float acc = 0.0f;
+    for(int h = 2*lane; h < head; h += 64)
+    {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(A + r*head + h));
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(dA + r*head + h));
+        acc = fmaf(a.x, g.x, fmaf(a.y, g.y, acc));
+    }
+    acc = warp_sum(acc);
+    if(lane == 0)
+    {
+        delta[r] = acc;
+        lse2[r] = lse[r]*LOG2E_F;
+    }
 }
+
+// dQ[r,h] += bf16(scale * acc[r,h]); the accumulator is split over two buffers.
+__global__ void bwd_dq_finish_kernel(int head, Index rows, Index half_rows, float scale,
+        const float *__restrict__ acc_lo, const float *__restrict__ acc_hi,
+        bf16 *__restrict__ dQ)
+{
+    const Index total = rows*head/4, stride = (Index)gridDim.x*blockDim.x;
+    for(Index x = (Index)blockIdx.x*blockDim.x + threadIdx.x; x < total; x += stride)
+    {
+        const Index e = 4*x, r = e/head;
+        const float *src = r < half_rows ? acc_lo + e : acc_hi + (e - half_rows*head);
+        const float4 a = *reinterpret_cast<const float4 *>(src);
+        uint2 old = *reinterpret_cast<const uint2 *>(dQ + e);
+        const float o0 = __uint_as_float(old.x << 16), o1 = __uint_as_float(old.x & 0xFFFF0000u);
+        const float o2 = __uint_as_float(old.y << 16), o3 = __uint_as_float(old.y & 0xFFFF0000u);
+        const float g0 = __bfloat162float(__float2bfloat16_rn(a.x*scale));
+        const float g1 = __bfloat162float(__float2bfloat16_rn(a.y*scale));
+        const float g2 = __bfloat162float(__float2bfloat16_rn(a.z*scale));
+        const float g3 = __bfloat162float(__float2bfloat16_rn(a.w*scale));
+        old.x = pack_bf16x2(o0 + g0, o1 + g1);
+        old.y = pack_bf16x2(o2 + g2, o3 + g3);
+        *reinterpret_cast<uint2 *>(dQ + e) = old;
+    }
+}
+
+template<int D>
+__device__ __forceinline__ void load_tile(uint8_t *dst, const CUtensorMap *map, uint64_t *bar,
+        int row)
+{
+#pragma unroll
+    for(int p = 0; p < D/64; ++p)
+    {
+        tma_load_2d(dst + p*(BLK*128), map, bar, 64*p, row);
+    }
+}
+
+// C[128 x 128] = A B^T with A, B both [128 rows][D] K-major tiles.
+template<int D>
+__device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, const uint8_t *a, const uint8_t *b)
+{
+    constexpr uint32_t idesc = idesc_bf16(BLK, BLK, 0, 0);
+    const uint32_t aa = smem_u32(a), ba = smem_u32(b);
+#pragma unroll
+    for(int ks = 0; ks < D/16; ++ks)
+    {
+        const uint32_t off = (ks >> 2)*(BLK*128) + (ks & 3)*32;
+        mma_ss(d_tmem, smem_desc_sw128(aa + off, 16, 1024), smem_desc_sw128(ba + off, 16, 1024),
+                idesc, ks > 0);
+    }
+}
+
+// C[128 x D] (+)= A B with A = bf16 [128 lanes x 128] in TMEM, stored as two
+// 32-column pieces at a_tmem and a_tmem + 64, and B = [128 rows][D] tile read
+// MN-major (rows are the contraction index).
+template<int D>
+__device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, const uint8_t *b,
+        bool accumulate)
+{
+    constexpr uint32_t idesc = idesc_bf16(BLK, D, 0, 1);
+    const uint32_t ba = smem_u32(b);
+#pragma unroll
+    for(int ks = 0; ks < BLK/16; ++ks)
+    {
+        const uint32_t a = a_tmem + (ks < 4 ? 8*ks : 64 + 8*(ks - 4));
+        mma_ts(d_tmem, a, smem_desc_sw128(ba + ks*2048, BLK*128, 1024), idesc,
+                (accumulate || ks > 0) ? 1u : 0u);
+    }
+}
+
+// dQ[128 q x D] = dS K with dS^T [128 key rows][128 q] in shared memory (MN-major A)
+// and K [128 key rows][D] (MN-major B).
+template<int D>
+__device__ __forceinline__ void issue_dq(uint32_t d_tmem, const uint8_t *ds, const uint8_t *k)
+{
+    constexpr uint32_t idesc = idesc_bf16(BLK, D, 1, 1);
+    const uint32_t aa = smem_u32(ds), ba = smem_u32(k);
+#pragma unroll
+    for(int ks = 0; ks < BLK/16; ++ks)
+    {
+        mma_ss(d_tmem, smem_desc_sw128(aa + ks*2048, BLK*128, 1024),
+                smem_desc_sw128(ba + ks*2048, BLK*128, 1024), idesc, ks > 0);
+    }
+}
+
+template<int D>
+__global__ void __launch_bounds__(THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
+        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
+        const __grid_constant__ CUtensorMap tmap_g, int seq, int batch, float scale_log2,
+        float scale, const bf16 *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
+        const float *__restrict__ delta, const float *__restrict__ lse2,
+        float *__restrict__ acc_lo, float *__restrict__ acc_hi, Index half_rows,
+        bf16 *__restrict__ dK, bf16 *__restrict__ dV, uint32_t *status)
+{
+    constexpr bool ALIAS = D == 128;     // dQ_i lives in the dP^T columns
+    extern __shared__ uint8_t smem_raw[];
+    Smem<D> &sm = *reinterpret_cast<Smem<D> *>(
+            (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nblk = seq/BLK;
+    const int kb = (int)(blockIdx.x/batch);      // early key blocks see most queries: first
+    const int b = (int)(blockIdx.x % batch);
+    const int row_base = b*seq;
+    volatile uint32_t *abort_flag = &sm.abort_flag;
+
+    if(tid == 0)
+    {
+        mbar_init(&sm.kv_full, 1);
+        for(int i = 0; i < 2; ++i)
+        {
+            mbar_init(&sm.q_full[i], 1);
+            mbar_init(&sm.q_empty[i], 1);
+            mbar_init(&sm.g_full[i], 1);
+            mbar_init(&sm.g_empty[i], 1);
+        }
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.dp_full, 1);
+        mbar_init(&sm.pds_full, 256);
+        mbar_init(&sm.dq_full, 1);
+        mbar_init(&sm.dq_empty, 128);
+        mbar_init(&sm.acc_full, 1);
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(status) != 0u ? 1u : 0u;
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_g);
+    }
+    if(warp == 1)
+    {
+        tmem_alloc(&sm.tmem_base, 512);
+    }
+    if(warp == 0)
+    {
+        int count = 0;
+        for(int base = 0; base < nblk; base += 32)
+        {
+            const int qb = base + lane;
+            uint8_t c = CLS_SKIP;
+            if(qb < nblk)
+            {
+                c = cls_tab[(size_t)qb*nblk + kb];
+                sm.cls[qb] = c;
+            }
+            count += __popc(__ballot_sync(0xffffffffu, c != CLS_SKIP));
+        }
+        if(lane == 0)
+        {
+            sm.nact = count;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const int nact = sm.abort_flag != 0u ? 0 : sm.nact;
+    constexpr uint32_t TILE_BYTES = Smem<D>::TILE_BYTES;
+    const uint32_t st_tm = tmem, dpt_tm = tmem + 128, dv_tm = tmem + 256, dk_tm = tmem + 256 + D;
+    const uint32_t dq_tm = ALIAS ? tmem + 128 : tmem + 384;
+
+    if(warp == 0)
+    {
+        // =============================== TMA producer ==========================
+        if(lane == 0 && nact > 0)
+        {
+            bool ok = true;
+            mbar_arrive_expect_tx(&sm.kv_full, 2*TILE_BYTES);
+            load_tile<D>(sm.k, &tmap_k, &sm.kv_full, row_base + kb*BLK);
+            load_tile<D>(sm.v, &tmap_v, &sm.kv_full, row_base + kb*BLK);
+            int n = 0;
+            for(int qb = 0; qb < nblk && ok; ++qb)
+            {
+                if(sm.cls[qb] == CLS_SKIP)
+                {
+                    continue;
+                }
+                const int st = n & 1;
+                const uint32_t ph = (uint32_t)(n >> 1) & 1u;
+                ok = mbar_wait(&sm.q_empty[st], ph ^ 1u, abort_flag);
+                if(!ok) break;
+                mbar_arrive_expect_tx(&sm.q_full[st], TILE_BYTES);
+                load_tile<D>(sm.q[st], &tmap_q, &sm.q_full[st], row_base + qb*BLK);
+                ok = mbar_wait(&sm.g_empty[st], ph ^ 1u, abort_flag);
+                if(!ok) break;
+                mbar_arrive_expect_tx(&sm.g_full[st], TILE_BYTES);
+                load_tile<D>(sm.g[st], &tmap_g, &sm.g_full[st], row_base + qb*BLK);
+                ++n;
+            }
+            if(!ok)
+            {
+                atomicExch(status, 11u);
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ================================ MMA issuer ===========================
+        if(lane == 0 && nact > 0)
+        {
+            bool ok = mbar_wait(&sm.kv_full, 0, abort_flag);
+            ok = ok && mbar_wait(&sm.q_full[0], 0, abort_flag);
+            if(ok)
+            {
+                tc_fence_after_sync();
+                issue_kmajor<D>(st_tm, sm.k, sm.q[0]);
+                tc_commit(&sm.s_full);
+            }
+            ok = ok && mbar_wait(&sm.g_full[0], 0, abort_flag);
+            if(ok)
+            {
+                tc_fence_after_sync();
+                issue_kmajor<D>(dpt_tm, sm.v, sm.g[0]);
+                tc_commit(&sm.dp_full);
+            }
+            for(int n = 0; n < nact && ok; ++n)
+            {
+                const int st = n & 1;
+                ok = mbar_wait(&sm.pds_full, (uint32_t)n & 1u, abort_flag);
+                if(!ok) break;
+                tc_fence_after_sync();
+                issue_ts<D>(dv_tm, st_tm, sm.g[st], n > 0);          // dV += P^T dO
+                tc_commit(&sm.g_empty[st]);
+                issue_ts<D>(dk_tm, dpt_tm, sm.q[st], n > 0);         // dK += dS^T Q
+                tc_commit(&sm.q_empty[st]);
+                if(!ALIAS && n > 0)
+                {
+                    ok = mbar_wait(&sm.dq_empty, (uint32_t)(n - 1) & 1u, abort_flag);
+                    if(!ok) break;
+                    tc_fence_after_sync();
+                }
+                issue_dq<D>(dq_tm, sm.ds, sm.k);                     // dQ_i = dS K
+                tc_commit(&sm.dq_full);
+                if(n + 1 < nact)
+                {
+                    const int s2 = (n + 1) & 1;
+                    const uint32_t ph = (uint32_t)((n + 1) >> 1) & 1u;
+                    ok = mbar_wait(&sm.q_full[s2], ph, abort_flag);
+                    if(!ok) break;
+                    tc_fence_after_sync();
+                    issue_kmajor<D>(st_tm, sm.k, sm.q[s2]);          // S^T of the next block
+                    tc_commit(&sm.s_full);
+                    ok = mbar_wait(&sm.g_full[s2], ph, abort_flag);
+                    if(ok && ALIAS)
+                    {
+                        ok = mbar_wait(&sm.dq_empty, (uint32_t)n & 1u, abort_flag);
+                    }
+                    if(!ok) break;
+                    tc_fence_after_sync();
+                    issue_kmajor<D>(dpt_tm, sm.v, sm.g[s2]);         // dP^T of the next block
+                    tc_commit(&sm.dp_full);
+                }
+                else
+                {
+                    tc_commit(&sm.acc_full);
+                }
+            }
+            if(!ok)
+            {
+                atomicExch(status, 12u);
+            }
+        }
+    }
+    else if(warp >= 4 && warp < 8)
+    {
+        // ================================ dQ drain =============================
+        const int r = 32*(warp & 3) + lane;
+        const uint32_t src = dq_tm + ((uint32_t)(32*(warp & 3)) << 16);
+        bool ok = true;
+        int n = 0;
+        for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
+        {
+            if(sm.cls[qb] == CLS_SKIP)
+            {
+                continue;
+            }
+            ok = mbar_wait(&sm.dq_full, (uint32_t)n & 1u, abort_flag);
+            if(!ok) break;
+            tc_fence_after_sync();
+            const Index R = (Index)row_base + (Index)qb*BLK + r;
+            float *dst = R < half_rows ? acc_lo + R*D : acc_hi + (R - half_rows)*D;
+#pragma unroll
+            for(int cc = 0; cc < D/32; ++cc)
+            {
+                uint32_t o[32];
+                tmem_ld32(src + 32*cc, o);
+                tmem_ld_wait();
+                if(cc == D/32 - 1)
+                {
+                    // every column is in registers: the MMA pipe may reuse them
+                    tc_fence_before_sync();
+                    mbar_arrive(&sm.dq_empty);
+                }
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+                {
+                    red_add_v4(dst + 32*cc + 4*j, __uint_as_float(o[4*j]),
+                            __uint_as_float(o[4*j + 1]), __uint_as_float(o[4*j + 2]),
+                            __uint_as_float(o[4*j + 3]));
+                }
+            }
+            ++n;
+        }
+        if(!ok && lane == 0)
+        {
+            atomicExch(status, 13u);
+        }
+    }
+    else if(warp >= 8)
+    {
+        // ================================= softmax =============================
+        const int ts = tid - 256;                     // 0..255
+        const int h = ts >> 7;                        // query-column half
+        const int r = 32*(warp & 3) + lane;           // key row inside the block
+        const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
+        bool ok = true;
+        int n = 0;
+        // delta / lse2 of the first active query block, one value per thread
+        int next_qb = 0;
+        while(next_qb < nblk && sm.cls[next_qb] == CLS_SKIP)
+        {
+            ++next_qb;
+        }
+        float stat = 0.0f;
+        if(next_qb < nblk && nact > 0)
+        {
+            const Index R = (Index)row_base + (Index)next_qb*BLK + (ts & 127);
+            stat = ts < 128 ? lse2[R] : delta[R];
+        }
+        for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
+        {
+            const uint8_t c = sm.cls[qb];
+            if(c == CLS_SKIP)
+            {
+                continue;
+            }
+            named_barrier_sync(1, 256);               // previous block's stats no longer read
+            sm.stats[ts >> 7][ts & 127] = stat;
+            named_barrier_sync(1, 256);
+            next_qb = qb + 1;
+            while(next_qb < nblk && sm.cls[next_qb] == CLS_SKIP)
+            {
+                ++next_qb;
+            }
+            if(next_qb < nblk)
+            {
+                const Index R = (Index)row_base + (Index)next_qb*BLK + (ts & 127);
+                stat = ts < 128 ? lse2[R] : delta[R];
+            }
+            ok = mbar_wait(&sm.s_full, (uint32_t)n & 1u, abort_flag);
+            ok = ok && mbar_wait(&sm.dp_full, (uint32_t)n & 1u, abort_flag);
+            if(!ok) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for(int c2 = 0; c2 < 2; ++c2)
+            {
+                const int col0 = 64*h + 32*c2;
+                uint32_t s[32], dp[32];
+                tmem_ld32(st_tm + lane_sel + col0, s);
+                tmem_ld32(dpt_tm + lane_sel + col0, dp);
+                tmem_ld_wait();
+                uint32_t pp[16], pd[16];
+#pragma unroll
+                for(int j = 0; j < 32; j += 2)
+                {
+                    float p[2], d[2];
+#pragma unroll
+                    for(int u = 0; u < 2; ++u)
+                    {
+                        const int qc = col0 + j + u;              // query inside the block
+                        const float l2 = sm.stats[0][qc], dl = sm.stats[1][qc];
+                        float x = fmaf(__uint_as_float(s[j + u]), scale_log2, -l2);
+                        bool dead = false;
+                        if(c == CLS_CAUSAL)
+                        {
+                            dead = r > qc;
+                        }
+                        else if(c == CLS_GENERIC)
+                        {
+                            const float bias = __bfloat162float(
+                                    mask[(size_t)(qb*BLK + qc)*seq + (size_t)kb*BLK + r]);
+                            dead = bias == -CUDART_INF_F;
+                            x = fmaf(bias, LOG2E_F, x);
+                        }
+                        p[u] = dead ? 0.0f : ex2(x);
+                        d[u] = p[u]*(__uint_as_float(dp[j + u]) - dl);
+                    }
+                    pp[j >> 1] = pack_bf16x2(p[0], p[1]);
+                    pd[j >> 1] = pack_bf16x2(d[0], d[1]);
+                }
+                tmem_st16(st_tm + lane_sel + 64*h + 16*c2, pp);
+                tmem_st16(dpt_tm + lane_sel + 64*h + 16*c2, pd);
+                // dS^T row r, query columns col0..col0+31: four 16-byte pieces of
+                // panel h, 128-byte swizzle
+                uint8_t *row = sm.ds + h*(BLK*128) + r*128;
+#pragma unroll
+                for(int i = 0; i < 4; ++i)
+                {
+                    const int ch = 4*c2 + i;
+                    *reinterpret_cast<uint4 *>(row + ((ch ^ (r & 7)) << 4)) =
+                            make_uint4(pd[4*i], pd[4*i + 1], pd[4*i + 2], pd[4*i + 3]);
+                }
+            }
+            tmem_st_wait();
+            fence_proxy_async();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.pds_full);
+            ++n;
+        }
+        // ---- epilogue: dV (half 0) / dK (half 1) += accumulators ------------------
+        if(ok && nact > 0)
+        {
+            ok = mbar_wait(&sm.acc_full, 0, abort_flag);
+        }
+        if(ok && nact > 0)
+        {
+            tc_fence_after_sync();
+            const Index R = (Index)row_base + (Index)kb*BLK + r;
+            uint4 *orow = reinterpret_cast<uint4 *>((h == 0 ? dV : dK) + R*D);
+            const uint32_t src = (h == 0 ? dv_tm : dk_tm) + lane_sel;
+            const float mult = h == 0 ? 1.0f : scale;
+#pragma unroll
+            for(int cc = 0; cc < D/32; ++cc)
+            {
+                uint32_t o[32];
+                tmem_ld32(src + 32*cc, o);
+                tmem_ld_wait();
+#pragma unroll
+                for(int g4 = 0; g4 < 4; ++g4)
+                {
+                    const uint4 prev = orow[4*cc + g4];
+                    const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
+                    uint32_t outw[4];
+#pragma unroll
+                    for(int e2 = 0; e2 < 4; ++e2)
+                    {
+                        const float a0 = __bfloat162float(__float2bfloat16_rn(
+                                __uint_as_float(o[8*g4 + 2*e2])*mult));
+                        const float a1 = __bfloat162float(__float2bfloat16_rn(
+                                __uint_as_float(o[8*g4 + 2*e2 + 1])*mult));
+                        outw[e2] = pack_bf16x2(__uint_as_float(pw[e2] << 16) + a0,
+                                __uint_as_float(pw[e2] & 0xFFFF0000u) + a1);
+                    }
+                    orow[4*cc + g4] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                }
+            }
+        }
+        if(!ok && lane == 0)
+        {
+            atomicExch(status, 14u);
+        }
+    }
+    // ---- tear-down ---------------------------------------------------------------
+    if(*abort_flag != 0u && tid == 0)
+    {
+        for(int i = 0; i < 64; ++i)
+        {
+            __nanosleep(1000);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if(warp == 1)
+    {
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+} // namespace bwd
+
+bool flash_bwd_sm100_supports(Index seq, Index head, Index batch)
+{
+    if(!((head == 64 || head == 128) && seq >= bwd::BLK && seq % bwd::BLK == 0
+            && seq/bwd::BLK <= bwd::MAX_BLOCKS && batch >= 1 && batch*seq < ((Index)1 << 31)))
+    {
+        return false;
+    }
+    // scratch_dV must hold status + class table + delta + lse2
+    const Index rows = batch*seq, nblk = seq/bwd::BLK;
+    const Index need = ((CLS_OFFSET + nblk*nblk + 255) & ~(Index)255) + 8*rows;
+    return need <= rows*head*2;
+}
+
+template<int D>
+static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const bf16 *Q,
+        const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask, const float *lse,
+        void *scratch_dK, void *scratch_dQ, void *scratch_dV, bf16 *dK, bf16 *dQ, bf16 *dV)
+{
+    using namespace bwd;
+    const Index rows = batch*seq;
+    const int nblk = (int)(seq/BLK);
+    uint8_t *sc = static_cast<uint8_t *>(scratch_dV);
+    const size_t stats_off = (CLS_OFFSET + (size_t)nblk*nblk + 255) & ~(size_t)255;
+    float *delta = reinterpret_cast<float *>(sc + stats_off);
+    float *lse2 = delta + rows;
+    float *acc_lo = static_cast<float *>(scratch_dQ), *acc_hi = static_cast<float *>(scratch_dK);
+    const Index half_rows = rows/2;
+    const size_t half_bytes = (size_t)rows*D*2;
+    if(cudaMemsetAsync(acc_lo, 0, half_bytes, s) != cudaSuccess
+            || cudaMemsetAsync(acc_hi, 0, half_bytes, s) != cudaSuccess)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    int st = launch_mask_classify(s, (int)seq, mask, sc);
+    if(st != NNTILE_B200_OK)
+    {
+        return st;
+    }
+    bwd_prep_kernel<<<(unsigned)((rows + 7)/8), 256, 0, s>>>(D, rows, A, dA, lse, delta, lse2);
+    if(launch_status() != NNTILE_B200_OK)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    CUtensorMap tk, tv, tq, tg;
+    if(!make_tmap_bf16_sw128(&tk, K, rows, D, BLK) || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK)
+            || !make_tmap_bf16_sw128(&tq, Q, rows, D, BLK)
+            || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK))
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    static const size_t smem_bytes = sizeof(Smem<D>) + 1024;
+    static const cudaError_t attr = cudaFuncSetAttribute(flash_bwd_kernel<D>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    if(attr != cudaSuccess)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    const float scale = 1.0f/sqrtf((float)D);
+    flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg,
+            (int)seq, (int)batch, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
+            acc_lo, acc_hi, half_rows, dK, dV, reinterpret_cast<uint32_t *>(sc));
+    if(launch_status() != NNTILE_B200_OK)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    bwd_dq_finish_kernel<<<grid_for(rows*D/4, 256), 256, 0, s>>>(D, rows, half_rows, scale,
+            acc_lo, acc_hi, dQ);
+    return launch_status();
+}
+
+int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
+        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
+        const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV, bf16 *dK,
+        bf16 *dQ, bf16 *dV)
+{
+    return head == 128
+            ? bwd_run<128>(s, seq, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scratch_dQ,
+                    scratch_dV, dK, dQ, dV)
+            : bwd_run<64>(s, seq, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scratch_dQ,
+                    scratch_dV, dK, dQ, dV);
+}
+
+} // namespace nb200

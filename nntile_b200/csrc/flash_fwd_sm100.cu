@@ -49,8 +49,6 @@ constexpr int MAX_BLOCKS = 512;      // seq <= 65536
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float LN2_F = 0.6931471805599453f;
 constexpr float RESCALE_STEP = 8.0f;
-enum : uint8_t { CLS_ZERO = 0, CLS_SKIP = 1, CLS_GENERIC = 2, CLS_CAUSAL = 3 };
-constexpr size_t CLS_OFFSET = 256;   // class table offset inside the scratch buffer
 
 // ------------------------------------------------------------ mask classifier
 // grid (key block, query block), 256 threads; also clears the status word.
@@ -601,8 +599,7 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
         return NNTILE_B200_E_LAUNCH;
     }
     const int nblk = (int)(seq/BLK);
-    mask_classify_kernel<<<dim3(nblk, nblk), 256, 0, s>>>((int)seq, nblk, mask, scratch);
-    if(launch_status() != NNTILE_B200_OK)
+    if(launch_mask_classify(s, (int)seq, mask, scratch) != NNTILE_B200_OK)
     {
         return NNTILE_B200_E_LAUNCH;
     }
@@ -620,12 +617,19 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     return launch_status();
 }
 
+int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *scratch)
+{
+    const int nblk = seq/fwd::BLK;
+    fwd::mask_classify_kernel<<<dim3(nblk, nblk), 256, 0, s>>>(seq, nblk, mask, scratch);
+    return launch_status();
+}
+
 int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A, void *scratch,
         size_t scratch_bytes)
 {
     const size_t nblk = (size_t)(seq/fwd::BLK);
-    if(scratch_bytes < fwd::CLS_OFFSET + nblk*nblk)
+    if(scratch_bytes < CLS_OFFSET + nblk*nblk)
     {
         return NNTILE_B200_E_SCRATCH;
     }
