@@ -188,6 +188,29 @@ int nntile_b200_decode_sdpa_bf16(nntile_b200_stream_t stream, int64_t head,
 size_t nntile_b200_decode_sdpa_workspace_bytes(int64_t head, int64_t length,
         int64_t batch, int64_t group, int64_t kv_heads);
 
+/* The same operation for callers that cannot hand over a workspace because they
+ * cannot allocate device memory where they run: the body of a StarPU codelet or
+ * of any other task-runtime worker callback (cudaMalloc there would serialise the
+ * device and go behind the runtime's memory accounting), or a C host that only
+ * holds device pointers someone else gave it.  No counterpart in the reference.
+ * The workspace is a fixed array inside the library image,
+ * nntile_b200_decode_sdpa_noalloc_max_bytes() bytes (32 MiB) of device memory that
+ * every GPU which loads the library keeps until the process exits; a problem whose
+ * nntile_b200_decode_sdpa_workspace_bytes(...) exceeds it is rejected with
+ * NNTILE_B200_E_SCRATCH.  The call allocates nothing and frees nothing.  The first
+ * call on each device looks up the array's device address (cudaGetSymbolAddress,
+ * with that device current) before it enqueues anything, so make that first call
+ * per device outside any stream capture.  All calls on one device share the one
+ * array and the array keeps whatever the last call left in it: two calls whose
+ * kernels may overlap on the GPU (different streams) race and must be ordered by
+ * the caller; calls on the same stream are safe.  Arguments, layouts and results
+ * are those of nntile_b200_decode_sdpa_bf16. */
+int nntile_b200_decode_sdpa_noalloc_bf16(nntile_b200_stream_t stream, int64_t head,
+        int64_t max_seq, int64_t length, int64_t batch, int64_t group,
+        int64_t kv_heads, const void *q, const void *Kcache, const void *Vcache,
+        void *out, float *lse_out);
+size_t nntile_b200_decode_sdpa_noalloc_max_bytes(void);
+
 /* ---------------------------------------------------------------------------
  * Tensor level: the tile loops of the fused path
  * ------------------------------------------------------------------------- */

@@ -507,3 +507,76 @@ extern "C" int nntile_b200_decode_sdpa_bf16(nntile_b200_stream_t stream, int64_t
             (int)heads, (int)heads, part_o, part_lse, (bf16 *)out, lse_out);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Decode without a caller-provided workspace
+// ---------------------------------------------------------------------------
+// Some hosts of this library have no way to obtain device memory for the
+// chunk-merge workspace: a StarPU codelet body (or any task-runtime worker
+// callback) runs where cudaMalloc is off limits - it would serialise the whole
+// device and bypass the runtime's memory accounting - and the reference's decode
+// path has no scratch handle to lend because this operation does not exist
+// there; a plain C host may simply hold device pointers it was given and no
+// allocator at all.  For them the workspace below is part of the library image:
+// a fixed array in device memory that every GPU which loads the library keeps
+// until the process exits.
+//
+// In host code `g_decode_scratch` is only a stand-in for the symbol, not a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+constexpr size_t DECODE_SCRATCH_BYTES = (size_t)32 << 20;       // 32 MiB per GPU
+constexpr int DECODE_MAX_DEVICES = 64;
+static __device__ __align__(256) unsigned char g_decode_scratch[DECODE_SCRATCH_BYTES];
+
+static void *g_decode_scratch_addr[DECODE_MAX_DEVICES];
+static std::atomic<int> g_decode_scratch_state[DECODE_MAX_DEVICES];   // 0 unset, 1 ready
+
+// Device address of the scratch array on the current device, or nullptr.
+static void *decode_scratch_for_current_device()
+{
+    int dev = -1;
+    if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= DECODE_MAX_DEVICES)
+    {
+        return nullptr;
+    }
+    if(g_decode_scratch_state[dev].load(std::memory_order_acquire) == 1)
+    {
+        return g_decode_scratch_addr[dev];
+    }
+    void *ptr = nullptr;
+    if(cudaGetSymbolAddress(&ptr, g_decode_scratch) != cudaSuccess || ptr == nullptr)
+    {
+        return nullptr;
+    }
+    // two threads racing here both obtain the same address for this device
+    g_decode_scratch_addr[dev] = ptr;
+    g_decode_scratch_state[dev].store(1, std::memory_order_release);
+    return ptr;
+}
+
+extern "C" size_t nntile_b200_decode_sdpa_noalloc_max_bytes(void)
+{
+    return DECODE_SCRATCH_BYTES;
+}
+
+extern "C" int nntile_b200_decode_sdpa_noalloc_bf16(nntile_b200_stream_t stream,
+        int64_t head, int64_t max_seq, int64_t length, int64_t batch, int64_t group,
+        int64_t kv_heads, const void *q, const void *Kcache, const void *Vcache, void *out,
+        float *lse_out)
+{
+    if(head > 0 && length > 0 && batch > 0 && group > 0 && kv_heads > 0
+            && nntile_b200_decode_sdpa_workspace_bytes(head, length, batch, group, kv_heads)
+                    > DECODE_SCRATCH_BYTES)
+    {
+        return NNTILE_B200_E_SCRATCH;      // problem too large for the built-in array
+    }
+    void *scratch = decode_scratch_for_current_device();
+    if(scratch == nullptr)
+    {
+        return NNTILE_B200_E_DEVICE;
+    }
+    // Every chunk slot the merge step reads is written by the chunk kernel of the
+    // same call first, so nothing in the array has to start at zero.
+    return nntile_b200_decode_sdpa_bf16(stream, head, max_seq, length, batch, group,
+            kv_heads, q, Kcache, Vcache, out, lse_out, scratch, DECODE_SCRATCH_BYTES);
+}
