@@ -5,7 +5,9 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libnntile_b200.so")
+# NNTILE_B200_LIB points at an alternative build of the same library (e.g. one
+# compiled with instrumentation); the default is the in-tree build.
+LIB_PATH = os.environ.get("NNTILE_B200_LIB") or os.path.join(_HERE, "csrc", "libnntile_b200.so")
 
 i64, f32, vp, sz = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 _pp = ctypes.POINTER(ctypes.c_void_p)

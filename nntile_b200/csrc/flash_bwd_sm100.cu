@@ -40,6 +40,18 @@ using namespace sm100;
 
 namespace bwd {
 
+// Optional cycle accounting of the roles (build with -DNB200_PROF).
+#ifdef NB200_PROF
+__device__ unsigned long long g_prof[24];
+#define PROF_T(var) const long long var = clock64()
+#define PROF_ADD(slot, a, b) atomicAdd(&g_prof[slot], (unsigned long long)((b) - (a)))
+#define PROF_INC(slot) atomicAdd(&g_prof[slot], 1ull)
+#else
+#define PROF_T(var)
+#define PROF_ADD(slot, a, b)
+#define PROF_INC(slot)
+#endif
+
 constexpr int BLK = 128;
 constexpr int THREADS = 512;
 constexpr int MAX_BLOCKS = 256;      // seq <= 32768
@@ -159,7 +171,9 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, const
 }
 
 // dQ[128 q x D] = dS K with dS^T [128 key rows][128 q] in shared memory (MN-major A)
-// and K [128 key rows][D] (MN-major B).
+// and K [128 key rows][D] (MN-major B) - or, with the operands swapped at head
+// 128, dQ^T[D x 128 q] = K^T dS^T.  Both tiles are read with the keys as the
+// contraction index, 16 key rows = 2048 bytes per step.
 template<int D>
 __device__ __forceinline__ void issue_dq(uint32_t d_tmem, const uint8_t *ds, const uint8_t *k)
 {
@@ -184,6 +198,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         bf16 *__restrict__ dK, bf16 *__restrict__ dV, uint32_t *status)
 {
     constexpr bool ALIAS = D == 128;     // dQ_i lives in the dP^T columns
+    // At head 128 the MMA produces dQ_i^T (lanes = head elements), so that the 32
+    // lanes of a drain warp add into 128 contiguous bytes: 8 times fewer L2
+    // reduction requests than one 16-byte piece per lane and row.
+    constexpr bool DQ_TRANSPOSED = D == 128;
     extern __shared__ uint8_t smem_raw[];
     Smem<D> &sm = *reinterpret_cast<Smem<D> *>(
             (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -306,9 +324,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             for(int n = 0; n < nact && ok; ++n)
             {
                 const int st = n & 1;
+                PROF_T(m0);
                 ok = mbar_wait(&sm.pds_full, (uint32_t)n & 1u, abort_flag);
                 if(!ok) break;
                 tc_fence_after_sync();
+                PROF_T(m1);
                 issue_ts<D>(dv_tm, st_tm, sm.g[st], n > 0);          // dV += P^T dO
                 tc_commit(&sm.g_empty[st]);
                 issue_ts<D>(dk_tm, dpt_tm, sm.q[st], n > 0);         // dK += dS^T Q
@@ -319,26 +339,48 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     if(!ok) break;
                     tc_fence_after_sync();
                 }
-                issue_dq<D>(dq_tm, sm.ds, sm.k);                     // dQ_i = dS K
+                if(DQ_TRANSPOSED)
+                {
+                    issue_dq<D>(dq_tm, sm.k, sm.ds);                 // dQ_i^T = K^T dS^T
+                }
+                else
+                {
+                    issue_dq<D>(dq_tm, sm.ds, sm.k);                 // dQ_i = dS K
+                }
                 tc_commit(&sm.dq_full);
+                PROF_T(m2);
+                PROF_ADD(0, m0, m1);        // MMA: wait for P^T / dS^T
+                PROF_ADD(1, m1, m2);        // MMA: issue dV, dK, dQ
+                PROF_INC(7);
                 if(n + 1 < nact)
                 {
                     const int s2 = (n + 1) & 1;
                     const uint32_t ph = (uint32_t)((n + 1) >> 1) & 1u;
+                    PROF_T(m3);
                     ok = mbar_wait(&sm.q_full[s2], ph, abort_flag);
                     if(!ok) break;
                     tc_fence_after_sync();
+                    PROF_T(m4);
                     issue_kmajor<D>(st_tm, sm.k, sm.q[s2]);          // S^T of the next block
                     tc_commit(&sm.s_full);
+                    PROF_T(m5);
                     ok = mbar_wait(&sm.g_full[s2], ph, abort_flag);
+                    PROF_T(m6);
                     if(ok && ALIAS)
                     {
                         ok = mbar_wait(&sm.dq_empty, (uint32_t)n & 1u, abort_flag);
                     }
                     if(!ok) break;
                     tc_fence_after_sync();
+                    PROF_T(m7);
                     issue_kmajor<D>(dpt_tm, sm.v, sm.g[s2]);         // dP^T of the next block
                     tc_commit(&sm.dp_full);
+                    PROF_T(m8);
+                    PROF_ADD(2, m3, m4);    // MMA: wait for Q tile
+                    PROF_ADD(3, m4, m5);    // MMA: issue S^T
+                    PROF_ADD(4, m5, m6);    // MMA: wait for dO tile
+                    PROF_ADD(5, m6, m7);    // MMA: wait for the dQ drain
+                    PROF_ADD(6, m7, m8);    // MMA: issue dP^T
                 }
                 else
                 {
@@ -364,31 +406,70 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             {
                 continue;
             }
+            PROF_T(d0);
             ok = mbar_wait(&sm.dq_full, (uint32_t)n & 1u, abort_flag);
             if(!ok) break;
             tc_fence_after_sync();
-            const Index R = (Index)row_base + (Index)qb*BLK + r;
-            float *dst = R < half_rows ? acc_lo + R*D : acc_hi + (R - half_rows)*D;
-#pragma unroll
-            for(int cc = 0; cc < D/32; ++cc)
+            PROF_T(d1);
+            if(DQ_TRANSPOSED)
             {
-                uint32_t o[32];
-                tmem_ld32(src + 32*cc, o);
-                tmem_ld_wait();
-                if(cc == D/32 - 1)
-                {
-                    // every column is in registers: the MMA pipe may reuse them
-                    tc_fence_before_sync();
-                    mbar_arrive(&sm.dq_empty);
-                }
+                // TMEM holds dQ_i^T: lane = head element r, column = query.  One red per
+                // query: the 32 lanes of a warp add 128 contiguous bytes of one row.
 #pragma unroll
-                for(int j = 0; j < 8; ++j)
+                for(int cc = 0; cc < BLK/32; ++cc)
                 {
-                    red_add_v4(dst + 32*cc + 4*j, __uint_as_float(o[4*j]),
-                            __uint_as_float(o[4*j + 1]), __uint_as_float(o[4*j + 2]),
-                            __uint_as_float(o[4*j + 3]));
+                    uint32_t o[32];
+                    tmem_ld32(src + 32*cc, o);
+                    tmem_ld_wait();
+                    if(cc == BLK/32 - 1)
+                    {
+                        // every column is in registers: the MMA pipe may reuse them
+                        tc_fence_before_sync();
+                        mbar_arrive(&sm.dq_empty);
+                    }
+                    // the accumulator is split at half_rows, a multiple of 64 rows
+                    const Index R0 = (Index)row_base + (Index)qb*BLK + 32*cc;
+                    float *dst = (R0 < half_rows ? acc_lo + R0*D : acc_hi + (R0 - half_rows)*D) + r;
+#pragma unroll
+                    for(int j = 0; j < 32; ++j)
+                    {
+                        red_add_f32(dst + (Index)j*D, __uint_as_float(o[j]));
+                    }
                 }
             }
+            else
+            {
+                const Index R = (Index)row_base + (Index)qb*BLK + r;
+                float *dst = R < half_rows ? acc_lo + R*D : acc_hi + (R - half_rows)*D;
+#pragma unroll
+                for(int cc = 0; cc < D/32; ++cc)
+                {
+                    uint32_t o[32];
+                    tmem_ld32(src + 32*cc, o);
+                    tmem_ld_wait();
+                    if(cc == D/32 - 1)
+                    {
+                        tc_fence_before_sync();
+                        mbar_arrive(&sm.dq_empty);
+                    }
+#pragma unroll
+                    for(int j = 0; j < 8; ++j)
+                    {
+                        red_add_v4(dst + 32*cc + 4*j, __uint_as_float(o[4*j]),
+                                __uint_as_float(o[4*j + 1]), __uint_as_float(o[4*j + 2]),
+                                __uint_as_float(o[4*j + 3]));
+                    }
+                }
+            }
+#ifdef NB200_PROF
+            if(r == 0)
+            {
+                PROF_T(d2);
+                PROF_ADD(8, d0, d1);        // drain: wait for dQ
+                PROF_ADD(9, d1, d2);        // drain: TMEM loads + reds
+                PROF_INC(10);
+            }
+#endif
             ++n;
         }
         if(!ok && lane == 0)
@@ -437,10 +518,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 const Index R = (Index)row_base + (Index)next_qb*BLK + (ts & 127);
                 stat = ts < 128 ? lse2[R] : delta[R];
             }
+            PROF_T(s0);
             ok = mbar_wait(&sm.s_full, (uint32_t)n & 1u, abort_flag);
+            PROF_T(s1);
             ok = ok && mbar_wait(&sm.dp_full, (uint32_t)n & 1u, abort_flag);
             if(!ok) break;
             tc_fence_after_sync();
+            PROF_T(s2);
 #pragma unroll
             for(int c2 = 0; c2 < 2; ++c2)
             {
@@ -495,6 +579,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             fence_proxy_async();
             tc_fence_before_sync();
             mbar_arrive(&sm.pds_full);
+#ifdef NB200_PROF
+            if(ts == 0)
+            {
+                PROF_T(s3);
+                PROF_ADD(12, s0, s1);       // softmax: wait for S^T
+                PROF_ADD(13, s1, s2);       // softmax: wait for dP^T
+                PROF_ADD(14, s2, s3);       // softmax: compute + stores
+                PROF_INC(15);
+            }
+#endif
             ++n;
         }
         // ---- epilogue: dV (half 0) / dK (half 1) += accumulators ------------------
@@ -557,6 +651,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 }
 
 } // namespace bwd
+
+#ifdef NB200_PROF
+extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out24, int reset)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out24, bwd::g_prof, sizeof(unsigned long long)*24);
+    if(reset)
+    {
+        unsigned long long z[24] = {0};
+        cudaMemcpyToSymbol(bwd::g_prof, z, sizeof(z));
+    }
+}
+#endif
 
 bool flash_bwd_sm100_supports(Index seq, Index head, Index batch)
 {

@@ -42,6 +42,17 @@ using namespace sm100;
 
 namespace fwd {
 
+// Optional cycle accounting of the roles (build with -DNB200_PROF): sums over all
+// CTAs of the cycles one softmax thread and the MMA thread spend in each phase.
+#ifdef NB200_PROF
+__device__ unsigned long long g_prof[16];
+#define PROF_T(var) const long long var = clock64()
+#define PROF_ADD(slot, a, b) atomicAdd(&g_prof[slot], (unsigned long long)((b) - (a)))
+#else
+#define PROF_T(var)
+#define PROF_ADD(slot, a, b)
+#endif
+
 constexpr int BLK = 128;             // query rows per tile and keys per block
 constexpr int THREADS = 384;         // 3 warpgroups: control, softmax 0, softmax 1
 constexpr int KV_STAGES = 2;
@@ -100,7 +111,7 @@ struct Smem
     uint64_t q_full[2];
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-    uint64_t s_full[2], p_full[2], o_full[2];
+    uint64_t s_full[2], p_half[2][2], o_full[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
     int nproc;
@@ -120,34 +131,60 @@ __device__ __forceinline__ void load_tile(uint8_t *dst, const CUtensorMap *map, 
     }
 }
 
-// S_t = Q_t K^T: D/16 k-steps, both operands K-major, 64-column panels.
+// S_t = Q_t K^T: D/16 k-steps, both operands K-major in 64-column panels.  The
+// issuing thread passes the low descriptor words of the two tiles; every step
+// only adds a constant to them.
 template<int D>
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, const uint8_t *q, const uint8_t *k)
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_t k_lo)
 {
     constexpr uint32_t idesc = idesc_bf16(BLK, BLK, 0, 0);
-    const uint32_t qa = smem_u32(q), ka = smem_u32(k);
+    constexpr uint32_t hi = smem_desc_hi(1024);
 #pragma unroll
     for(int ks = 0; ks < D/16; ++ks)
     {
-        const uint32_t off = (ks >> 2)*(BLK*128) + (ks & 3)*32;
-        mma_ss(d_tmem, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
-                idesc, ks > 0);
+        const uint32_t off = (uint32_t)(((ks >> 2)*(BLK*128) + (ks & 3)*32) >> 4);
+        if(ks == 0)
+        {
+            mma_ss_c<false>(d_tmem, smem_desc_join(q_lo + off, hi), smem_desc_join(k_lo + off, hi),
+                    idesc);
+        }
+        else
+        {
+            mma_ss_c<true>(d_tmem, smem_desc_join(q_lo + off, hi), smem_desc_join(k_lo + off, hi),
+                    idesc);
+        }
     }
 }
 
-// O_t (+)= P_t V: 8 k-steps of 16 keys; P from TMEM (8 columns per step), V
-// MN-major: 16 key rows = 2048 bytes per step, next 64 head columns 16 KB away.
-template<int D>
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, const uint8_t *v,
+// O_t (+)= P_t V, half of the 8 k-steps of 16 keys: P from TMEM (8 columns per
+// step), V MN-major: 16 key rows = 2048 bytes per step (the next 64 head columns,
+// 16 KB away, are the leading offset inside v_lo).
+template<int D, int HALF>
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo,
         bool accumulate)
 {
     constexpr uint32_t idesc = idesc_bf16(BLK, D, 0, 1);
-    const uint32_t va = smem_u32(v);
+    constexpr uint32_t hi = smem_desc_hi(1024);
 #pragma unroll
-    for(int ks = 0; ks < BLK/16; ++ks)
+    for(int k4 = 0; k4 < BLK/32; ++k4)
     {
-        mma_ts(d_tmem, p_tmem + 8*ks, smem_desc_sw128(va + ks*2048, BLK*128, 1024), idesc,
-                (accumulate || ks > 0) ? 1u : 0u);
+        const int ks = 4*HALF + k4;
+        const uint64_t vd = smem_desc_join(v_lo + (uint32_t)((ks*2048) >> 4), hi);
+        if(HALF == 0 && k4 == 0)
+        {
+            if(accumulate)
+            {
+                mma_ts_c<true>(d_tmem, p_tmem + 8*ks, vd, idesc);
+            }
+            else
+            {
+                mma_ts_c<false>(d_tmem, p_tmem + 8*ks, vd, idesc);
+            }
+        }
+        else
+        {
+            mma_ts_c<true>(d_tmem, p_tmem + 8*ks, vd, idesc);
+        }
     }
 }
 
@@ -178,7 +215,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         {
             mbar_init(&sm.q_full[i], 1);
             mbar_init(&sm.s_full[i], 1);
-            mbar_init(&sm.p_full[i], 128);
+            mbar_init(&sm.p_half[i][0], 128);
+            mbar_init(&sm.p_half[i][1], 128);
             mbar_init(&sm.o_full[i], 1);
         }
         for(int i = 0; i < KV_STAGES; ++i)
@@ -288,6 +326,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             bool ok = true;
             const uint32_t s_tm[2] = {tmem, tmem + 128};
             const uint32_t o_tm[2] = {tmem + 256, tmem + 256 + D};
+            // low descriptor words of every operand tile (K-major: leading offset
+            // unused; MN-major V: next 64 head columns one 16 KB panel away)
+            const uint32_t q_lo[2] = {smem_desc_lo(smem_u32(sm.q[0]), 16),
+                                      smem_desc_lo(smem_u32(sm.q[1]), 16)};
+            const uint32_t k_lo[KV_STAGES] = {smem_desc_lo(smem_u32(sm.k[0]), 16),
+                                              smem_desc_lo(smem_u32(sm.k[1]), 16)};
+            const uint32_t v_lo[KV_STAGES] = {smem_desc_lo(smem_u32(sm.v[0]), BLK*128),
+                                              smem_desc_lo(smem_u32(sm.v[1]), BLK*128)};
             int qk_done[2] = {-1, -1};          // last iteration whose QK_t was issued
             int n_pv[2] = {0, 0};               // PV steps issued per tile
             int k_waited = -1, k_released = -1;
@@ -311,7 +357,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     k_waited = it;
                     tc_fence_after_sync();
                 }
-                issue_qk<D>(s_tm[t], sm.q[t], sm.k[st]);
+                issue_qk<D>(s_tm[t], q_lo[t], k_lo[st]);
                 tc_commit(&sm.s_full[t]);
                 qk_done[t] = it;
                 // release the K stage once every tile that needs this block has issued
@@ -342,11 +388,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     {
                         continue;
                     }
-                    ok = mbar_wait(&sm.p_full[t], p_phase[t], abort_flag);
+                    PROF_T(mt0);
+                    ok = mbar_wait(&sm.p_half[t][0], p_phase[t], abort_flag);
+                    if(!ok) break;
+                    tc_fence_after_sync();
+                    PROF_T(mt1);
+                    issue_pv<D, 0>(o_tm[t], s_tm[t], v_lo[st], n_pv[t] > 0);
+                    PROF_T(mt2);
+                    ok = mbar_wait(&sm.p_half[t][1], p_phase[t], abort_flag);
                     if(!ok) break;
                     p_phase[t] ^= 1u;
                     tc_fence_after_sync();
-                    issue_pv<D>(o_tm[t], s_tm[t], sm.v[st], n_pv[t] > 0);
+                    PROF_T(mt3);
+                    issue_pv<D, 1>(o_tm[t], s_tm[t], v_lo[st], true);
+                    PROF_T(mt4);
+                    PROF_ADD(8, mt0, mt1);      // MMA thread: wait for first half of P
+                    PROF_ADD(9, mt1, mt2);      // issue 4 PV steps
+                    PROF_ADD(10, mt2, mt3);     // wait for second half of P
+                    PROF_ADD(11, mt3, mt4);     // issue 4 PV steps
+#ifdef NB200_PROF
+                    atomicAdd(&g_prof[12], 1ull);
+#endif
                     ++n_pv[t];
                     if(t == last_t)
                     {
@@ -391,20 +453,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             {
                 continue;
             }
+            PROF_T(pt0);
             ok = mbar_wait(&sm.s_full[t], s_phase, abort_flag);
             if(!ok) break;
             s_phase ^= 1u;
             tc_fence_after_sync();
+            PROF_T(pt1);
             uint32_t s[4][32];
             tmem_ld32(s_tm, s[0]);
             tmem_ld32(s_tm + 32, s[1]);
             tmem_ld32(s_tm + 64, s[2]);
             tmem_ld32(s_tm + 96, s[3]);
             tmem_ld_wait();
+            PROF_T(pt2);
             // ---- bias; x = s*scale_log2 + bias*log2e is formed lazily below ------
-            float top_raw = -CUDART_INF_F;
+            float top_raw;
             if(c == CLS_GENERIC)
             {
+                top_raw = -CUDART_INF_F;
                 const bf16 *mrow = mask + (size_t)(qb*BLK + r)*seq + (size_t)sm.list[it]*BLK;
 #pragma unroll
                 for(int g = 0; g < 16; ++g)
@@ -425,18 +491,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             else
             {
-#pragma unroll
-                for(int j = 0; j < 128; ++j)
+                if(c == CLS_CAUSAL)
                 {
-                    if(c == CLS_CAUSAL && j > r)
+#pragma unroll
+                    for(int j = 0; j < 128; ++j)
                     {
-                        s[j >> 5][j & 31] = __float_as_uint(-CUDART_INF_F);
+                        if(j > r)
+                        {
+                            s[j >> 5][j & 31] = __float_as_uint(-CUDART_INF_F);
+                        }
                     }
-                    top_raw = fmaxf(top_raw, __uint_as_float(s[j >> 5][j & 31]));
                 }
+                // four independent chains of three-input max
+                float t0 = -CUDART_INF_F, t1 = t0, t2 = t0, t3 = t0;
+#pragma unroll
+                for(int q4 = 0; q4 < 4; ++q4)
+                {
+#pragma unroll
+                    for(int j = 0; j < 32; j += 8)
+                    {
+                        t0 = fmax3(t0, __uint_as_float(s[q4][j]), __uint_as_float(s[q4][j + 1]));
+                        t1 = fmax3(t1, __uint_as_float(s[q4][j + 2]), __uint_as_float(s[q4][j + 3]));
+                        t2 = fmax3(t2, __uint_as_float(s[q4][j + 4]), __uint_as_float(s[q4][j + 5]));
+                        t3 = fmax3(t3, __uint_as_float(s[q4][j + 6]), __uint_as_float(s[q4][j + 7]));
+                    }
+                }
+                top_raw = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
             }
             const float mul = c == CLS_GENERIC ? 1.0f : scale_log2;
             const float m_blk = top_raw*mul;               // -inf stays -inf
+            PROF_T(pt3);
             // ---- lazy rescale ----------------------------------------------------
             const bool grow = m_blk > m_used + RESCALE_STEP;   // true on the first finite block
             const float m_new = grow ? m_blk : m_used;
@@ -461,26 +545,54 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             l *= alpha;
             m_used = m_new;
             const float neg_ref = m_used == -CUDART_INF_F ? 0.0f : -m_used;
-            // ---- P = exp2(x - m), row sum, bf16 pack, back into the S columns -----
-            float part = 0.0f;
+            PROF_T(pt4);
+            // ---- P = exp2(x - m), row sum, bf16 pack, back into the S columns; the
+            // two halves of the row are handed to the MMA warp separately ------------
+            const uint64_t mul2 = pack_f32x2(mul, mul), ref2 = pack_f32x2(neg_ref, neg_ref);
+            uint64_t sum_a = 0ull, sum_b = 0ull;          // two packed chains = four sums
 #pragma unroll
             for(int h = 0; h < 2; ++h)
             {
                 uint32_t pk[32];
 #pragma unroll
-                for(int j = 0; j < 32; ++j)
+                for(int j = 0; j < 32; j += 2)
                 {
-                    const float p0 = ex2(fmaf(__uint_as_float(s[2*h + (j >> 4)][(2*j) & 31]), mul, neg_ref));
-                    const float p1 = ex2(fmaf(__uint_as_float(s[2*h + (j >> 4)][(2*j + 1) & 31]), mul, neg_ref));
-                    part += p0 + p1;
-                    pk[j] = pack_bf16x2(p0, p1);
+                    const uint32_t *src = &s[2*h + (j >> 4)][(2*j) & 31];
+                    float xa0, xa1, xb0, xb1;
+                    unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(src[0]), __uint_as_float(src[1])),
+                            mul2, ref2), xa0, xa1);
+                    unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(src[2]), __uint_as_float(src[3])),
+                            mul2, ref2), xb0, xb1);
+                    const float pa0 = ex2(xa0), pa1 = ex2(xa1), pb0 = ex2(xb0), pb1 = ex2(xb1);
+                    sum_a = fadd2(sum_a, pack_f32x2(pa0, pa1));
+                    sum_b = fadd2(sum_b, pack_f32x2(pb0, pb1));
+                    pk[j] = pack_bf16x2(pa0, pa1);
+                    pk[j + 1] = pack_bf16x2(pb0, pb1);
                 }
                 tmem_st32(s_tm + 32*h, pk);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][h]);
             }
-            l += part;
-            tmem_st_wait();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.p_full[t]);
+            {
+                float a0, a1, b0, b1;
+                unpack_f32x2(fadd2(sum_a, sum_b), a0, a1);
+                b0 = a0 + a1;
+                b1 = 0.0f;
+                l += b0 + b1;
+            }
+#ifdef NB200_PROF
+            if(r == 0 && t == 0)
+            {
+                PROF_T(pt5);
+                PROF_ADD(0, pt0, pt1);      // wait for S
+                PROF_ADD(1, pt1, pt2);      // tcgen05.ld of the row
+                PROF_ADD(2, pt2, pt3);      // mask + max
+                PROF_ADD(3, pt3, pt4);      // rescale decision (+ O round trip)
+                PROF_ADD(4, pt4, pt5);      // exp2, pack, store, arrive
+                atomicAdd(&g_prof[5], 1ull);
+            }
+#endif
             ++n;
         }
         // ---- epilogue: normalise, merge with the stored (lse, A), store ---------
@@ -578,6 +690,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 } // namespace fwd
+
+#ifdef NB200_PROF
+extern "C" void nntile_b200_debug_prof(unsigned long long *out16, int reset)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out16, fwd::g_prof, sizeof(unsigned long long)*16);
+    if(reset)
+    {
+        unsigned long long z[16] = {0};
+        cudaMemcpyToSymbol(fwd::g_prof, z, sizeof(z));
+    }
+}
+#endif
 
 bool flash_fwd_sm100_supports(Index seq, Index head, Index batch)
 {

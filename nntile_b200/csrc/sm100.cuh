@@ -184,6 +184,28 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     return d;
 }
 
+// The same descriptor split into its two 32-bit words so that the issuing thread
+// can keep one low word per tile and step through k by adding a constant: the
+// high word depends only on the stride offset, the low word is
+// (address >> 4) | (leading offset >> 4) << 16.  Adding (bytes >> 4) to the low word
+// moves the start address as long as the tile stays below 256 KB of shared memory.
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes)
+{
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes)
+{
+    return ((saddr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo, uint32_t hi)
+{
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulate:
 //   bits 4-5 D format (1 = f32)   bits 7-9 A format (1 = bf16)   bits 10-12 B format
 //   bit 15 A major (0 = K, 1 = MN)   bit 16 B major   bits 17-22 N>>3   bits 24-28 M>>4
@@ -215,6 +237,47 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Variants whose accumulate flag is a compile-time constant (no setp on a register).
+template<bool ACC>
+__device__ __forceinline__ void mma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+        uint32_t idesc)
+{
+    if(ACC)
+    {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
+    }
+    else
+    {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
+    }
+}
+
+template<bool ACC>
+__device__ __forceinline__ void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+        uint32_t idesc)
+{
+    if(ACC)
+    {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc) : "memory");
+    }
+    else
+    {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc) : "memory");
+    }
 }
 
 // ------------------------------------------------------- TMEM <-> registers
@@ -283,6 +346,11 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthread
     asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(nthreads) : "memory");
 }
 
+__device__ __forceinline__ void red_add_f32(float *addr, float a)
+{
+    asm volatile("red.global.add.f32 [%0], %1;" :: "l"(addr), "f"(a) : "memory");
+}
+
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d)
 {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
@@ -301,11 +369,72 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
     return r;
 }
 
+// Three-input max and two-wide packed fp32 arithmetic (one instruction for two
+// lanes of a 64-bit register pair), both new with sm_100.
+__device__ __forceinline__ float fmax3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ float ex2(float x)
 {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// exp2 of two packed fp32 values on the FMA and ALU pipes, for when the MUFU unit
+// (16 ex2 per clock per SM) is the limiter: round to the nearest integer n with
+// the 1.5*2^23 trick, a cubic for 2^f on f in [-0.5, 0.5] (relative error 1e-4,
+// well below the bf16 rounding of the probabilities), then n is added into the
+// exponent field.  Inputs below -126 (including -inf) give a value <= 2^-126.
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2)
+{
+    float x0, x1;
+    unpack_f32x2(x2, x0, x1);
+    x2 = pack_f32x2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);
+    const uint64_t t2 = fadd2(x2, magic);
+    const uint64_t n2 = fadd2(t2, pack_f32x2(-12582912.0f, -12582912.0f));
+    const uint64_t f2 = ffma2(n2, pack_f32x2(-1.0f, -1.0f), x2);
+    uint64_t p2 = ffma2(pack_f32x2(0.05583828f, 0.05583828f), f2,
+            pack_f32x2(0.24263948f, 0.24263948f));
+    p2 = ffma2(p2, f2, pack_f32x2(0.69313675f, 0.69313675f));
+    p2 = ffma2(p2, f2, pack_f32x2(0.99992454f, 0.99992454f));
+    float p0, p1, t0, t1;
+    unpack_f32x2(p2, p0, p1);
+    unpack_f32x2(t2, t0, t1);
+    p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+    return pack_f32x2(p0, p1);
 }
 
 } // namespace sm100
