@@ -44,12 +44,16 @@ namespace bwd {
 #ifdef NB200_PROF
 __device__ unsigned long long g_prof[24];
 #define PROF_T(var) const long long var = clock64()
-#define PROF_ADD(slot, a, b) atomicAdd(&g_prof[slot], (unsigned long long)((b) - (a)))
-#define PROF_INC(slot) atomicAdd(&g_prof[slot], 1ull)
+#define PROF_DECL unsigned long long prof_loc[24]; for(int i_ = 0; i_ < 24; ++i_) prof_loc[i_] = 0
+#define PROF_ADD(slot, a, b) prof_loc[slot] += (unsigned long long)((b) - (a))
+#define PROF_INC(slot) prof_loc[slot] += 1ull
+#define PROF_FLUSH for(int i_ = 0; i_ < 24; ++i_) if(prof_loc[i_]) atomicAdd(&g_prof[i_], prof_loc[i_])
 #else
 #define PROF_T(var)
+#define PROF_DECL
 #define PROF_ADD(slot, a, b)
 #define PROF_INC(slot)
+#define PROF_FLUSH
 #endif
 
 constexpr int BLK = 128;
@@ -66,17 +70,18 @@ struct Smem
     uint8_t q[2][TILE_BYTES];
     uint8_t g[2][TILE_BYTES];            // dO
     uint8_t ds[BLK*BLK*2];               // dS^T, [key rows][query cols], swizzled
-    float stats[2][BLK];                 // [0] lse*log2e, [1] delta of the query block
+    float stats[2][2][BLK];              // per Q stage: [0] -lse*log2e, [1] -delta
     uint64_t kv_full;
     uint64_t q_full[2], q_empty[2], g_full[2], g_empty[2];
-    uint64_t s_full, dp_full, pds_full, dq_full, dq_empty, acc_full;
+    uint64_t s_full, dp_full, p_full, ds_full, dq_full, dq_empty, acc_full;
     uint32_t tmem_base;
     uint32_t abort_flag;
     int nact;
     uint8_t cls[MAX_BLOCKS];             // class of (query block qb, this key block)
 };
 
-// delta[r] = sum_h A[r,h]*dA[r,h];  lse2[r] = lse[r]*log2(e)
+// delta[r] = -sum_h A[r,h]*dA[r,h];  lse2[r] = -lse[r]*log2(e)  (both are only ever
+// used negated by the main kernel)
 __global__ void bwd_prep_kernel(int head, Index rows, const bf16 *__restrict__ A,
         const bf16 *__restrict__ dA, const float *__restrict__ lse,
         float *__restrict__ delta, float *__restrict__ lse2)
@@ -97,8 +102,8 @@ __global__ void bwd_prep_kernel(int head, Index rows, const bf16 *__restrict__ A
     acc = warp_sum(acc);
     if(lane == 0)
     {
-        delta[r] = acc;
-        lse2[r] = lse[r]*LOG2E_F;
+        delta[r] = -acc;
+        lse2[r] = -lse[r]*LOG2E_F;
     }
 }
 
@@ -137,18 +142,31 @@ __device__ __forceinline__ void load_tile(uint8_t *dst, const CUtensorMap *map, 
     }
 }
 
+// The issue helpers build each operand descriptor as (low word of the tile) +
+// constant, high word constant (sm100.cuh), so that one MMA costs the issuing
+// thread two integer adds.
+
 // C[128 x 128] = A B^T with A, B both [128 rows][D] K-major tiles.
 template<int D>
 __device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, const uint8_t *a, const uint8_t *b)
 {
     constexpr uint32_t idesc = idesc_bf16(BLK, BLK, 0, 0);
-    const uint32_t aa = smem_u32(a), ba = smem_u32(b);
+    constexpr uint32_t hi = smem_desc_hi(1024);
+    const uint32_t a_lo = smem_desc_lo(smem_u32(a), 16), b_lo = smem_desc_lo(smem_u32(b), 16);
 #pragma unroll
     for(int ks = 0; ks < D/16; ++ks)
     {
-        const uint32_t off = (ks >> 2)*(BLK*128) + (ks & 3)*32;
-        mma_ss(d_tmem, smem_desc_sw128(aa + off, 16, 1024), smem_desc_sw128(ba + off, 16, 1024),
-                idesc, ks > 0);
+        const uint32_t off = (uint32_t)(((ks >> 2)*(BLK*128) + (ks & 3)*32) >> 4);
+        if(ks == 0)
+        {
+            mma_ss_c<false>(d_tmem, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi),
+                    idesc);
+        }
+        else
+        {
+            mma_ss_c<true>(d_tmem, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi),
+                    idesc);
+        }
     }
 }
 
@@ -160,13 +178,21 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, const
         bool accumulate)
 {
     constexpr uint32_t idesc = idesc_bf16(BLK, D, 0, 1);
-    const uint32_t ba = smem_u32(b);
+    constexpr uint32_t hi = smem_desc_hi(1024);
+    const uint32_t b_lo = smem_desc_lo(smem_u32(b), BLK*128);
+    if(accumulate)
+    {
+        mma_ts_c<true>(d_tmem, a_tmem, smem_desc_join(b_lo, hi), idesc);
+    }
+    else
+    {
+        mma_ts_c<false>(d_tmem, a_tmem, smem_desc_join(b_lo, hi), idesc);
+    }
 #pragma unroll
-    for(int ks = 0; ks < BLK/16; ++ks)
+    for(int ks = 1; ks < BLK/16; ++ks)
     {
         const uint32_t a = a_tmem + (ks < 4 ? 8*ks : 64 + 8*(ks - 4));
-        mma_ts(d_tmem, a, smem_desc_sw128(ba + ks*2048, BLK*128, 1024), idesc,
-                (accumulate || ks > 0) ? 1u : 0u);
+        mma_ts_c<true>(d_tmem, a, smem_desc_join(b_lo + (uint32_t)((ks*2048) >> 4), hi), idesc);
     }
 }
 
@@ -178,12 +204,23 @@ template<int D>
 __device__ __forceinline__ void issue_dq(uint32_t d_tmem, const uint8_t *ds, const uint8_t *k)
 {
     constexpr uint32_t idesc = idesc_bf16(BLK, D, 1, 1);
-    const uint32_t aa = smem_u32(ds), ba = smem_u32(k);
+    constexpr uint32_t hi = smem_desc_hi(1024);
+    const uint32_t a_lo = smem_desc_lo(smem_u32(ds), BLK*128);
+    const uint32_t b_lo = smem_desc_lo(smem_u32(k), BLK*128);
 #pragma unroll
     for(int ks = 0; ks < BLK/16; ++ks)
     {
-        mma_ss(d_tmem, smem_desc_sw128(aa + ks*2048, BLK*128, 1024),
-                smem_desc_sw128(ba + ks*2048, BLK*128, 1024), idesc, ks > 0);
+        const uint32_t off = (uint32_t)((ks*2048) >> 4);
+        if(ks == 0)
+        {
+            mma_ss_c<false>(d_tmem, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi),
+                    idesc);
+        }
+        else
+        {
+            mma_ss_c<true>(d_tmem, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi),
+                    idesc);
+        }
     }
 }
 
@@ -202,15 +239,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // lanes of a drain warp add into 128 contiguous bytes: 8 times fewer L2
     // reduction requests than one 16-byte piece per lane and row.
     constexpr bool DQ_TRANSPOSED = D == 128;
-    extern __shared__ uint8_t smem_raw[];
-    Smem<D> &sm = *reinterpret_cast<Smem<D> *>(
-            (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    // The tiles need 1024-byte alignment (128-byte swizzle atoms) and at head 128 the
+    // structure fills the 227 KB of a CTA to within 600 bytes, so there is no room
+    // for a round-up: the alignment is requested from the toolchain and verified.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    if((smem_u32(smem_raw) & 1023u) != 0u)
+    {
+        if(threadIdx.x == 0)
+        {
+            atomicExch(status, 20u);
+        }
+        return;
+    }
+    Smem<D> &sm = *reinterpret_cast<Smem<D> *>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nblk = seq/BLK;
     const int kb = (int)(blockIdx.x/batch);      // early key blocks see most queries: first
     const int b = (int)(blockIdx.x % batch);
     const int row_base = b*seq;
     volatile uint32_t *abort_flag = &sm.abort_flag;
+    PROF_DECL;
 
     if(tid == 0)
     {
@@ -224,7 +272,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
         mbar_init(&sm.s_full, 1);
         mbar_init(&sm.dp_full, 1);
-        mbar_init(&sm.pds_full, 256);
+        mbar_init(&sm.p_full, 256);
+        mbar_init(&sm.ds_full, 256);
         mbar_init(&sm.dq_full, 1);
         mbar_init(&sm.dq_empty, 128);
         mbar_init(&sm.acc_full, 1);
@@ -267,6 +316,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t st_tm = tmem, dpt_tm = tmem + 128, dv_tm = tmem + 256, dk_tm = tmem + 256 + D;
     const uint32_t dq_tm = ALIAS ? tmem + 128 : tmem + 384;
 
+    if(warp < 4)
+    {
+    // control warpgroup: hand registers to the drain warpgroup, which then holds a
+    // whole dQ_i tile (128 columns) and frees the TMEM columns after one load round
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if(warp == 0)
     {
         // =============================== TMA producer ==========================
@@ -287,8 +341,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 const uint32_t ph = (uint32_t)(n >> 1) & 1u;
                 ok = mbar_wait(&sm.q_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
-                mbar_arrive_expect_tx(&sm.q_full[st], TILE_BYTES);
+                mbar_arrive_expect_tx(&sm.q_full[st], TILE_BYTES + 2*BLK*4);
                 load_tile<D>(sm.q[st], &tmap_q, &sm.q_full[st], row_base + qb*BLK);
+                bulk_load_1d(sm.stats[st][0], lse2 + (Index)row_base + (Index)qb*BLK, BLK*4,
+                        &sm.q_full[st]);
+                bulk_load_1d(sm.stats[st][1], delta + (Index)row_base + (Index)qb*BLK, BLK*4,
+                        &sm.q_full[st]);
                 ok = mbar_wait(&sm.g_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
                 mbar_arrive_expect_tx(&sm.g_full[st], TILE_BYTES);
@@ -306,31 +364,52 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // ================================ MMA issuer ===========================
         if(lane == 0 && nact > 0)
         {
+            // Issue order.  The loop-carried chain is
+            //   dS^T(n) -> dK(n), dQ(n) -> drain -> dP^T(n+1) -> dS^T(n+1);
+            // dV(n+1) is slotted into the drain window and S^T(n+2) behind dP^T(n+1),
+            // where the softmax warps are busy with dS^T(n+1), so the tensor pipe
+            // has work whenever the chain leaves it idle.
             bool ok = mbar_wait(&sm.kv_full, 0, abort_flag);
             ok = ok && mbar_wait(&sm.q_full[0], 0, abort_flag);
             if(ok)
             {
                 tc_fence_after_sync();
-                issue_kmajor<D>(st_tm, sm.k, sm.q[0]);
+                issue_kmajor<D>(st_tm, sm.k, sm.q[0]);               // S^T(0)
                 tc_commit(&sm.s_full);
             }
             ok = ok && mbar_wait(&sm.g_full[0], 0, abort_flag);
             if(ok)
             {
                 tc_fence_after_sync();
-                issue_kmajor<D>(dpt_tm, sm.v, sm.g[0]);
+                issue_kmajor<D>(dpt_tm, sm.v, sm.g[0]);              // dP^T(0)
                 tc_commit(&sm.dp_full);
             }
+            ok = ok && mbar_wait(&sm.p_full, 0, abort_flag);
+            if(ok)
+            {
+                tc_fence_after_sync();
+                issue_ts<D>(dv_tm, st_tm, sm.g[0], false);           // dV = P^T(0) dO
+                tc_commit(&sm.g_empty[0]);
+            }
+            if(ok && nact > 1)
+            {
+                ok = mbar_wait(&sm.q_full[1], 0, abort_flag);
+                if(ok)
+                {
+                    tc_fence_after_sync();
+                    issue_kmajor<D>(st_tm, sm.k, sm.q[1]);           // S^T(1)
+                    tc_commit(&sm.s_full);
+                }
+            }
+            bool s_pending = false;
             for(int n = 0; n < nact && ok; ++n)
             {
-                const int st = n & 1;
+                const int st = n & 1, s2 = (n + 1) & 1;
                 PROF_T(m0);
-                ok = mbar_wait(&sm.pds_full, (uint32_t)n & 1u, abort_flag);
+                ok = mbar_wait(&sm.ds_full, (uint32_t)n & 1u, abort_flag);
                 if(!ok) break;
                 tc_fence_after_sync();
                 PROF_T(m1);
-                issue_ts<D>(dv_tm, st_tm, sm.g[st], n > 0);          // dV += P^T dO
-                tc_commit(&sm.g_empty[st]);
                 issue_ts<D>(dk_tm, dpt_tm, sm.q[st], n > 0);         // dK += dS^T Q
                 tc_commit(&sm.q_empty[st]);
                 if(!ALIAS && n > 0)
@@ -348,44 +427,78 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     issue_dq<D>(dq_tm, sm.ds, sm.k);                 // dQ_i = dS K
                 }
                 tc_commit(&sm.dq_full);
-                PROF_T(m2);
-                PROF_ADD(0, m0, m1);        // MMA: wait for P^T / dS^T
-                PROF_ADD(1, m1, m2);        // MMA: issue dV, dK, dQ
-                PROF_INC(7);
-                if(n + 1 < nact)
+                if(s_pending)
                 {
-                    const int s2 = (n + 1) & 1;
-                    const uint32_t ph = (uint32_t)((n + 1) >> 1) & 1u;
-                    PROF_T(m3);
-                    ok = mbar_wait(&sm.q_full[s2], ph, abort_flag);
+                    ok = mbar_wait(&sm.q_full[s2], (uint32_t)((n + 1) >> 1) & 1u, abort_flag);
                     if(!ok) break;
                     tc_fence_after_sync();
-                    PROF_T(m4);
-                    issue_kmajor<D>(st_tm, sm.k, sm.q[s2]);          // S^T of the next block
+                    issue_kmajor<D>(st_tm, sm.k, sm.q[s2]);          // the deferred S^T(n+1)
                     tc_commit(&sm.s_full);
-                    PROF_T(m5);
-                    ok = mbar_wait(&sm.g_full[s2], ph, abort_flag);
-                    PROF_T(m6);
-                    if(ok && ALIAS)
-                    {
-                        ok = mbar_wait(&sm.dq_empty, (uint32_t)n & 1u, abort_flag);
-                    }
-                    if(!ok) break;
-                    tc_fence_after_sync();
-                    PROF_T(m7);
-                    issue_kmajor<D>(dpt_tm, sm.v, sm.g[s2]);         // dP^T of the next block
-                    tc_commit(&sm.dp_full);
-                    PROF_T(m8);
-                    PROF_ADD(2, m3, m4);    // MMA: wait for Q tile
-                    PROF_ADD(3, m4, m5);    // MMA: issue S^T
-                    PROF_ADD(4, m5, m6);    // MMA: wait for dO tile
-                    PROF_ADD(5, m6, m7);    // MMA: wait for the dQ drain
-                    PROF_ADD(6, m7, m8);    // MMA: issue dP^T
+                    s_pending = false;
                 }
-                else
+                PROF_T(m2);
+                PROF_ADD(0, m0, m1);        // MMA: wait for dS^T
+                PROF_ADD(1, m1, m2);        // MMA: issue dK, dQ
+                PROF_INC(7);
+                if(n + 1 >= nact)
                 {
                     tc_commit(&sm.acc_full);
+                    break;
                 }
+                const uint32_t ph1 = (uint32_t)((n + 1) >> 1) & 1u;
+                ok = mbar_wait(&sm.g_full[s2], ph1, abort_flag);
+                if(!ok) break;
+                PROF_T(m3);
+                // dV(n+1) goes first only if P^T(n+1) is already there; otherwise the
+                // chain (dP^T) must not wait for it
+                bool dv_issued = false;
+                if(mbar_try_wait(&sm.p_full, (uint32_t)(n + 1) & 1u))
+                {
+                    tc_fence_after_sync();
+                    issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);       // dV += P^T(n+1) dO
+                    dv_issued = true;
+                }
+                PROF_T(m4);
+                PROF_T(m5);
+                if(ALIAS)
+                {
+                    ok = mbar_wait(&sm.dq_empty, (uint32_t)n & 1u, abort_flag);
+                    if(!ok) break;
+                    tc_fence_after_sync();
+                }
+                PROF_T(m6);
+                issue_kmajor<D>(dpt_tm, sm.v, sm.g[s2]);             // dP^T(n+1)
+                tc_commit(&sm.dp_full);
+                if(!dv_issued)
+                {
+                    ok = mbar_wait(&sm.p_full, (uint32_t)(n + 1) & 1u, abort_flag);
+                    if(!ok) break;
+                    tc_fence_after_sync();
+                    issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);       // dV += P^T(n+1) dO
+                }
+                tc_commit(&sm.g_empty[s2]);
+                PROF_T(m7);
+                if(n + 2 < nact)
+                {
+                    // Q(n+2) reuses the stage dK(n) has just released; if its copy has
+                    // not landed yet, S^T(n+2) is issued after the next dK, dQ instead
+                    if(mbar_try_wait(&sm.q_full[st], (uint32_t)((n + 2) >> 1) & 1u))
+                    {
+                        tc_fence_after_sync();
+                        issue_kmajor<D>(st_tm, sm.k, sm.q[st]);      // S^T(n+2)
+                        tc_commit(&sm.s_full);
+                    }
+                    else
+                    {
+                        s_pending = true;
+                    }
+                }
+                PROF_T(m8);
+                PROF_ADD(2, m3, m4);        // MMA: wait for P^T(n+1)
+                PROF_ADD(3, m4, m5);        // MMA: issue dV
+                PROF_ADD(4, m5, m6);        // MMA: wait for the dQ drain
+                PROF_ADD(5, m6, m7);        // MMA: issue dP^T
+                PROF_ADD(6, m7, m8);        // MMA: wait Q + issue S^T(n+2)
             }
             if(!ok)
             {
@@ -393,8 +506,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
         }
     }
-    else if(warp >= 4 && warp < 8)
+    }
+    else if(warp < 8)
     {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
         // ================================ dQ drain =============================
         const int r = 32*(warp & 3) + lane;
         const uint32_t src = dq_tm + ((uint32_t)(32*(warp & 3)) << 16);
@@ -413,27 +528,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             PROF_T(d1);
             if(DQ_TRANSPOSED)
             {
-                // TMEM holds dQ_i^T: lane = head element r, column = query.  One red per
-                // query: the 32 lanes of a warp add 128 contiguous bytes of one row.
+                // TMEM holds dQ_i^T: lane = head element r, column = query.  The whole
+                // tile goes into registers in one round, the columns are handed back
+                // to the MMA pipe at once, and only then the reductions are issued:
+                // one red per query, the 32 lanes of a warp adding 128 contiguous bytes.
+                uint32_t o[4][32];
+                tmem_ld32(src, o[0]);
+                tmem_ld32(src + 32, o[1]);
+                tmem_ld32(src + 64, o[2]);
+                tmem_ld32(src + 96, o[3]);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.dq_empty);
 #pragma unroll
                 for(int cc = 0; cc < BLK/32; ++cc)
                 {
-                    uint32_t o[32];
-                    tmem_ld32(src + 32*cc, o);
-                    tmem_ld_wait();
-                    if(cc == BLK/32 - 1)
-                    {
-                        // every column is in registers: the MMA pipe may reuse them
-                        tc_fence_before_sync();
-                        mbar_arrive(&sm.dq_empty);
-                    }
                     // the accumulator is split at half_rows, a multiple of 64 rows
                     const Index R0 = (Index)row_base + (Index)qb*BLK + 32*cc;
                     float *dst = (R0 < half_rows ? acc_lo + R0*D : acc_hi + (R0 - half_rows)*D) + r;
 #pragma unroll
                     for(int j = 0; j < 32; ++j)
                     {
-                        red_add_f32(dst + (Index)j*D, __uint_as_float(o[j]));
+                        red_add_f32(dst + (Index)j*D, __uint_as_float(o[cc][j]));
                     }
                 }
             }
@@ -477,7 +593,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             atomicExch(status, 13u);
         }
     }
-    else if(warp >= 8)
+    else
     {
         // ================================= softmax =============================
         const int ts = tid - 256;                     // 0..255
@@ -486,18 +602,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
         bool ok = true;
         int n = 0;
-        // delta / lse2 of the first active query block, one value per thread
-        int next_qb = 0;
-        while(next_qb < nblk && sm.cls[next_qb] == CLS_SKIP)
-        {
-            ++next_qb;
-        }
-        float stat = 0.0f;
-        if(next_qb < nblk && nact > 0)
-        {
-            const Index R = (Index)row_base + (Index)next_qb*BLK + (ts & 127);
-            stat = ts < 128 ? lse2[R] : delta[R];
-        }
         for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
         {
             const uint8_t c = sm.cls[qb];
@@ -505,66 +609,120 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             {
                 continue;
             }
-            named_barrier_sync(1, 256);               // previous block's stats no longer read
-            sm.stats[ts >> 7][ts & 127] = stat;
-            named_barrier_sync(1, 256);
-            next_qb = qb + 1;
-            while(next_qb < nblk && sm.cls[next_qb] == CLS_SKIP)
-            {
-                ++next_qb;
-            }
-            if(next_qb < nblk)
-            {
-                const Index R = (Index)row_base + (Index)next_qb*BLK + (ts & 127);
-                stat = ts < 128 ? lse2[R] : delta[R];
-            }
+            // -lse*log2e and -delta of the query block arrive with the Q tile (bulk
+            // copies on the same barrier); this thread handles 64 of the 128 queries
+            ok = mbar_wait(&sm.q_full[n & 1], (uint32_t)(n >> 1) & 1u, abort_flag);
+            if(!ok) break;
+            const float4 *nl4 = reinterpret_cast<const float4 *>(&sm.stats[n & 1][0][64*h]);
+            const float4 *nd4 = reinterpret_cast<const float4 *>(&sm.stats[n & 1][1][64*h]);
+            // ---- phase A: P^T = exp2(S^T*c - lse2 [+ bias]) for this thread's 64 query
+            // columns, kept as packed bf16 in registers and written over the S^T
+            // columns; needs S^T only, so it overlaps the MMAs of the previous block
             PROF_T(s0);
             ok = mbar_wait(&sm.s_full, (uint32_t)n & 1u, abort_flag);
-            PROF_T(s1);
-            ok = ok && mbar_wait(&sm.dp_full, (uint32_t)n & 1u, abort_flag);
             if(!ok) break;
             tc_fence_after_sync();
-            PROF_T(s2);
-#pragma unroll
-            for(int c2 = 0; c2 < 2; ++c2)
+            PROF_T(s1);
+            uint32_t pk[32];
             {
-                const int col0 = 64*h + 32*c2;
-                uint32_t s[32], dp[32];
-                tmem_ld32(st_tm + lane_sel + col0, s);
-                tmem_ld32(dpt_tm + lane_sel + col0, dp);
+                uint32_t s[2][32];
+                tmem_ld32(st_tm + lane_sel + 64*h, s[0]);
+                tmem_ld32(st_tm + lane_sel + 64*h + 32, s[1]);
                 tmem_ld_wait();
-                uint32_t pp[16], pd[16];
+                const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
 #pragma unroll
-                for(int j = 0; j < 32; j += 2)
+                for(int c2 = 0; c2 < 2; ++c2)
                 {
-                    float p[2], d[2];
 #pragma unroll
-                    for(int u = 0; u < 2; ++u)
+                    for(int j = 0; j < 32; j += 4)
                     {
-                        const int qc = col0 + j + u;              // query inside the block
-                        const float l2 = sm.stats[0][qc], dl = sm.stats[1][qc];
-                        float x = fmaf(__uint_as_float(s[j + u]), scale_log2, -l2);
-                        bool dead = false;
+                        const int qc = 64*h + 32*c2 + j;          // query inside the block
+                        const float4 nl = nl4[(32*c2 + j) >> 2];
+                        float x[4];
+                        unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(s[c2][j]),
+                                __uint_as_float(s[c2][j + 1])), scale2, pack_f32x2(nl.x, nl.y)),
+                                x[0], x[1]);
+                        unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(s[c2][j + 2]),
+                                __uint_as_float(s[c2][j + 3])), scale2, pack_f32x2(nl.z, nl.w)),
+                                x[2], x[3]);
                         if(c == CLS_CAUSAL)
                         {
-                            dead = r > qc;
+#pragma unroll
+                            for(int u = 0; u < 4; ++u)
+                            {
+                                x[u] = r > qc + u ? -CUDART_INF_F : x[u];
+                            }
                         }
                         else if(c == CLS_GENERIC)
                         {
-                            const float bias = __bfloat162float(
-                                    mask[(size_t)(qb*BLK + qc)*seq + (size_t)kb*BLK + r]);
-                            dead = bias == -CUDART_INF_F;
-                            x = fmaf(bias, LOG2E_F, x);
+#pragma unroll
+                            for(int u = 0; u < 4; ++u)
+                            {
+                                const float bias = __bfloat162float(
+                                        mask[(size_t)(qb*BLK + qc + u)*seq + (size_t)kb*BLK + r]);
+                                x[u] = bias == -CUDART_INF_F ? -CUDART_INF_F
+                                                             : fmaf(bias, LOG2E_F, x[u]);
+                            }
                         }
-                        p[u] = dead ? 0.0f : ex2(x);
-                        d[u] = p[u]*(__uint_as_float(dp[j + u]) - dl);
+                        // half of the exponentials on the MUFU unit, half as a cubic on
+                        // the FMA pipe: 16384 ex2 per block pair would otherwise hold
+                        // the 16-per-clock unit for as long as two of the five MMAs
+                        float e2, e3;
+#ifdef NB200_BWD_POLY_EXP
+                        unpack_f32x2(ex2_poly2(pack_f32x2(x[2], x[3])), e2, e3);
+#else
+                        e2 = ex2(x[2]);
+                        e3 = ex2(x[3]);
+#endif
+                        pk[(32*c2 + j) >> 1] = pack_bf16x2(ex2(x[0]), ex2(x[1]));
+                        pk[((32*c2 + j) >> 1) + 1] = pack_bf16x2(e2, e3);
                     }
-                    pp[j >> 1] = pack_bf16x2(p[0], p[1]);
-                    pd[j >> 1] = pack_bf16x2(d[0], d[1]);
                 }
-                tmem_st16(st_tm + lane_sel + 64*h + 16*c2, pp);
+            }
+            {
+                uint32_t (&lo)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[0]);
+                uint32_t (&hi)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[16]);
+                tmem_st16(st_tm + lane_sel + 64*h, lo);
+                tmem_st16(st_tm + lane_sel + 64*h + 16, hi);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_full);
+            // ---- phase B: dS^T = P^T o (dP^T - delta), to TMEM (for dK) and to shared
+            // memory (for dQ); this is the part on the loop-carried chain
+            PROF_T(s2);
+            ok = mbar_wait(&sm.dp_full, (uint32_t)n & 1u, abort_flag);
+            if(!ok) break;
+            tc_fence_after_sync();
+            PROF_T(s3);
+            uint32_t dp2[2][32];
+            tmem_ld32(dpt_tm + lane_sel + 64*h, dp2[0]);
+            tmem_ld32(dpt_tm + lane_sel + 64*h + 32, dp2[1]);
+            tmem_ld_wait();
+#pragma unroll
+            for(int c2 = 0; c2 < 2; ++c2)
+            {
+                uint32_t pd[16];
+                const uint32_t (&dp)[32] = dp2[c2];
+#pragma unroll
+                for(int j = 0; j < 32; j += 4)
+                {
+                    const float4 nd = nd4[(32*c2 + j) >> 2];
+                    const uint32_t w0 = pk[(32*c2 + j) >> 1], w1 = pk[((32*c2 + j) >> 1) + 1];
+                    float d[4];
+                    unpack_f32x2(fmul2(pack_f32x2(__uint_as_float(w0 << 16),
+                            __uint_as_float(w0 & 0xFFFF0000u)),
+                            fadd2(pack_f32x2(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])),
+                                    pack_f32x2(nd.x, nd.y))), d[0], d[1]);
+                    unpack_f32x2(fmul2(pack_f32x2(__uint_as_float(w1 << 16),
+                            __uint_as_float(w1 & 0xFFFF0000u)),
+                            fadd2(pack_f32x2(__uint_as_float(dp[j + 2]), __uint_as_float(dp[j + 3])),
+                                    pack_f32x2(nd.z, nd.w))), d[2], d[3]);
+                    pd[j >> 1] = pack_bf16x2(d[0], d[1]);
+                    pd[(j >> 1) + 1] = pack_bf16x2(d[2], d[3]);
+                }
                 tmem_st16(dpt_tm + lane_sel + 64*h + 16*c2, pd);
-                // dS^T row r, query columns col0..col0+31: four 16-byte pieces of
+                // dS^T row r, query columns 64h+32c2 .. +31: four 16-byte pieces of
                 // panel h, 128-byte swizzle
                 uint8_t *row = sm.ds + h*(BLK*128) + r*128;
 #pragma unroll
@@ -578,14 +736,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             tmem_st_wait();
             fence_proxy_async();
             tc_fence_before_sync();
-            mbar_arrive(&sm.pds_full);
+            mbar_arrive(&sm.ds_full);
 #ifdef NB200_PROF
             if(ts == 0)
             {
-                PROF_T(s3);
+                PROF_T(s4);
                 PROF_ADD(12, s0, s1);       // softmax: wait for S^T
-                PROF_ADD(13, s1, s2);       // softmax: wait for dP^T
-                PROF_ADD(14, s2, s3);       // softmax: compute + stores
+                PROF_ADD(13, s1, s2);       // softmax: phase A
+                PROF_ADD(14, s2, s3);       // softmax: wait for dP^T
+                PROF_ADD(16, s3, s4);       // softmax: phase B
                 PROF_INC(15);
             }
 #endif
@@ -635,6 +794,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
     }
     // ---- tear-down ---------------------------------------------------------------
+    PROF_FLUSH;
     if(*abort_flag != 0u && tid == 0)
     {
         for(int i = 0; i < 64; ++i)
@@ -715,7 +875,7 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     {
         return NNTILE_B200_E_LAUNCH;
     }
-    static const size_t smem_bytes = sizeof(Smem<D>) + 1024;
+    static const size_t smem_bytes = sizeof(Smem<D>);
     static const cudaError_t attr = cudaFuncSetAttribute(flash_bwd_kernel<D>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if(attr != cudaSuccess)

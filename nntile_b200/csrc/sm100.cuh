@@ -122,6 +122,17 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
            "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// Untiled bulk copy global -> this CTA's shared memory, completion on an mbarrier;
+// both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_src,
+        uint32_t bytes, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        :: "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes),
+           "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map)
 {
     asm volatile("prefetch.tensormap [%0];" :: "l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -348,7 +359,9 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthread
 
 __device__ __forceinline__ void red_add_f32(float *addr, float a)
 {
+#ifndef NB200_EXP_NORED      // timing experiment only: results are wrong without it
     asm volatile("red.global.add.f32 [%0], %1;" :: "l"(addr), "f"(a) : "memory");
+#endif
 }
 
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d)
@@ -394,6 +407,13 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c)
 {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("mul.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
 
