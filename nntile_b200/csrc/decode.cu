@@ -404,12 +404,19 @@ static DecodePlan decode_plan(Index head, Index length, Index batch, Index group
 {
     DecodePlan p;
     p.fast = (head == 64 || head == 128) && group >= 1 && group <= 8;
-    // chunks of 512 keys, 64 chunks at most (longer caches get longer chunks)
-    Index rows = 512;
-    while((length + rows - 1)/rows > 64)
-    {
-        rows *= 2;
-    }
+    // Chunk length: long chunks amortise the per-CTA prologue and merge (measured on
+    // config 5: 512 keys per CTA 5.2 TB/s, 1024 5.6, 2048 6.0, 4096 5.5), as long as
+    // about four to five waves of CTAs (148 SMs x 3 resident) remain for balance.
+    // The fast kernel shares a chunk among the query heads of a group, the generic
+    // one runs one CTA row per query head.
+    const Index units = p.fast ? batch*kv_heads : batch*group*kv_heads;
+    Index nsplit = (2048 + units - 1)/units;
+    const Index max_split = (length + 255)/256;          // at least 256 keys per chunk
+    if(nsplit > max_split) nsplit = max_split;
+    if(nsplit > 64) nsplit = 64;
+    if(nsplit < 1) nsplit = 1;
+    Index rows = (length + nsplit - 1)/nsplit;
+    rows = (rows + 63)/64*64;                            // whole steps of the 4 warps
     p.rows_per_cta = (int)rows;
     p.nsplit = (int)((length + rows - 1)/rows);
     if(p.nsplit < 1) p.nsplit = 1;

@@ -70,8 +70,8 @@ def test_noalloc_decode_matches_the_workspace_entry_point_twice_in_a_row():
 def test_noalloc_decode_rejects_what_does_not_fit():
     lib = _lib.load()
     null = ctypes.c_void_p(0)
-    # 64 x 32 heads against 32768 cached positions needs more than the 32 MiB array
-    D, L, B, G, H = 128, 32768, 64, 4, 8
+    # 4096 x 64 query heads need 135 MB of chunk results, more than the 32 MiB array
+    D, L, B, G, H = 128, 1024, 4096, 8, 8
     assert lib.nntile_b200_decode_sdpa_workspace_bytes(D, L, B, G, H) > (32 << 20)
     st = lib.nntile_b200_decode_sdpa_noalloc_bf16(null, D, L, L, B, G, H, null, null, null,
                                                   null, null)
