@@ -69,3 +69,19 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libnntile_b200.so")
     with pytest.raises(_lib.LibraryMissing):
         _lib.load()
+
+
+def test_cpp_shims_compile_and_reach_the_library(lib, tmp_path):
+    """include/nntile_b200/kernel_shims.hh re-creates nntile::kernel::<op>::cuda<T>;
+    tests/shim_check.cc instantiates every shim and calls it with null pointers,
+    which the library rejects before any launch (no GPU needed)."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    exe = str(tmp_path / "shim_check")
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-o", exe,
+                    os.path.join(ROOT, "tests", "shim_check.cc"), _lib.LIB_PATH,
+                    "-Wl,-rpath," + libdir], check=True)
+    assert subprocess.run([exe]).returncode == 0
