@@ -506,7 +506,41 @@ def run_extras(torch, ops, lib, dev, peaks, args):
     out["c4_long_context"] = run_c4(torch, ops, lib, dev, steps)
     # ---- config 5: decode, HBM-bound
     out["c5_decode"] = run_decode(torch, ops, dev, peaks, C5, steps*4, 5)
+    # ---- library comparator (context only, not the product): cuDNN's SDPA as the
+    # reference reaches it - additive bf16 bias, no causal flag - and with the flag
+    out["cudnn_comparator_c3"] = run_cudnn_comparator(torch, dev)
     return out
+
+
+def run_cudnn_comparator(torch, dev):
+    """cuDNN fused attention through torch (the Blackwell kernel the reference's
+    flash_sdpa_{fwd,bwd}_cudnn wrappers reach), config 3 shape, same FLOP convention.
+    'bias' is the reference's call pattern (mask as additive bias, causal flag off,
+    src/kernel/flash_sdpa_fwd_cudnn/cuda.cc:103-110) without its scratch copy, merge
+    and add_inplace passes; 'causal_flag' is cuDNN's own best case."""
+    import torch.nn.functional as F
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        B, H, S, D = C3["batch"], C3["group"]*C3["kv_heads"], C3["seq"], C3["head"]
+        g = torch.Generator(device=dev).manual_seed(9)
+        q, k, v = (torch.randn((B, H, S, D), generator=g, device=dev).to(torch.bfloat16)
+                   .requires_grad_(True) for _ in range(3))
+        do = torch.randn((B, H, S, D), generator=g, device=dev).to(torch.bfloat16)
+        bias = causal_mask_tile(S, "diag", dev).view(1, 1, S, S)
+        W = B*H*S*S*D
+        res = {}
+        for name, kw in (("bias", dict(attn_mask=bias)), ("causal_flag", dict(is_causal=True))):
+            with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+                def step():
+                    o = F.scaled_dot_product_attention(q, k, v, **kw)
+                    o.backward(do)
+                ms, _, _ = time_steps(torch, step, 5, 3)
+            ms /= 5
+            res[name] = {"ms_per_step": ms, "tflops": 7.0*W/(ms*1e-3)/1e12}
+        res["note"] = "library comparator; causal-convention FLOPs (the bias form executes all S^2)"
+        return res
+    except Exception as exc:          # comparator only: never fail the benchmark
+        return {"unavailable": repr(exc)[:200]}
 
 
 def run_decode(torch, ops, dev, peaks, c5, steps, warmup):

@@ -623,7 +623,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if(!ok) break;
             tc_fence_after_sync();
             PROF_T(s1);
-            uint32_t pk[32];
+            uint32_t pk[2][16];                   // [32-column half][packed pair]
             {
                 uint32_t s[2][32];
                 tmem_ld32(st_tm + lane_sel + 64*h, s[0]);
@@ -674,16 +674,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         e2 = ex2(x[2]);
                         e3 = ex2(x[3]);
 #endif
-                        pk[(32*c2 + j) >> 1] = pack_bf16x2(ex2(x[0]), ex2(x[1]));
-                        pk[((32*c2 + j) >> 1) + 1] = pack_bf16x2(e2, e3);
+                        pk[c2][j >> 1] = pack_bf16x2(ex2(x[0]), ex2(x[1]));
+                        pk[c2][(j >> 1) + 1] = pack_bf16x2(e2, e3);
                     }
                 }
             }
             {
-                uint32_t (&lo)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[0]);
-                uint32_t (&hi)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[16]);
-                tmem_st16(st_tm + lane_sel + 64*h, lo);
-                tmem_st16(st_tm + lane_sel + 64*h + 16, hi);
+                tmem_st16(st_tm + lane_sel + 64*h, pk[0]);
+                tmem_st16(st_tm + lane_sel + 64*h + 16, pk[1]);
             }
             tmem_st_wait();
             tc_fence_before_sync();
@@ -708,7 +706,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 for(int j = 0; j < 32; j += 4)
                 {
                     const float4 nd = nd4[(32*c2 + j) >> 2];
-                    const uint32_t w0 = pk[(32*c2 + j) >> 1], w1 = pk[((32*c2 + j) >> 1) + 1];
+                    const uint32_t w0 = pk[c2][j >> 1], w1 = pk[c2][(j >> 1) + 1];
                     float d[4];
                     unpack_f32x2(fmul2(pack_f32x2(__uint_as_float(w0 << 16),
                             __uint_as_float(w0 & 0xFFFF0000u)),

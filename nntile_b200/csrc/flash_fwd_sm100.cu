@@ -281,7 +281,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if(warp < 4)
     {
     // control warpgroup: give registers away, then producer / MMA issuer / idle
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if(warp == 0)
     {
         // =============================== TMA producer ==========================
@@ -338,7 +338,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             int n_pv[2] = {0, 0};               // PV steps issued per tile
             int k_waited = -1, k_released = -1;
             uint32_t p_phase[2] = {0, 0};
-            for(int t = 0; t < 2 && ok; ++t)
+#pragma unroll
+            for(int t = 0; t < 2; ++t)
             {
                 if(sm.nact[t] > 0)
                 {
@@ -372,7 +373,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             for(int it = 0; it < nproc && ok; ++it)
             {
                 const int st = it % KV_STAGES;
-                for(int t = 0; t < 2 && ok; ++t)
+    #pragma unroll
+            for(int t = 0; t < 2; ++t)
                 {
                     if(sm.cls[t][it] != CLS_SKIP && qk_done[t] < it)
                     {
@@ -382,7 +384,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if(!ok) break;
                 ok = mbar_wait(&sm.v_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag);
                 const int last_t = sm.cls[1][it] != CLS_SKIP ? 1 : 0;
-                for(int t = 0; t < 2 && ok; ++t)
+    #pragma unroll
+            for(int t = 0; t < 2; ++t)
                 {
                     if(sm.cls[t][it] == CLS_SKIP)
                     {
@@ -433,7 +436,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
     else
     {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ============================= softmax groups ==========================
         const int t = (warp - 4) >> 2;                    // query tile of this group
         const int r = 32*(warp & 3) + lane;               // row inside the tile
