@@ -319,7 +319,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     if(warp < 4)
     {
     // control warpgroup: hand registers to the drain warpgroup, which then holds a
-    // whole dQ_i tile (128 columns) and frees the TMEM columns after one load round
+    // whole dQ_i tile (128 columns) and frees the TMEM columns after one load round.
+    // An increase is only ever served from registers a warpgroup of this CTA gave
+    // up, and waits for them without a bound, so released must equal requested:
+    // launch 128 x 512 = control 96 x 128 + drain 160 x 128 + softmax 128 x 256.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if(warp == 0)
     {

@@ -280,7 +280,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     if(warp < 4)
     {
-    // control warpgroup: give registers away, then producer / MMA issuer / idle
+    // control warpgroup: give registers away, then producer / MMA issuer / idle.
+    // An increase is only ever served from registers a warpgroup of this CTA gave
+    // up, and waits for them without a bound, so released must equal requested:
+    // launch 168 x 384 = control 56 x 128 + softmax 224 x 256.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if(warp == 0)
     {
