@@ -40,6 +40,36 @@ enum : uint8_t
 // [query block][key block] at CLS_OFFSET.
 constexpr size_t CLS_OFFSET = 256;
 
+// CTA numbering shared by the two tcgen05 kernels.  CTAs are numbered group by
+// group; a group is `gsz` consecutive batch entries whose tensors (and, in the
+// backward, fp32 dQ accumulator) fit the L2 cache together, so the CTAs that are
+// resident at the same time re-read each other's K/V (forward) or Q/dO and
+// accumulator lines (backward) from L2 instead of DRAM.  Inside a group the
+// numbering is unit-major (unit = key block or query-tile pair), so the caller
+// can put heavy units first.
+constexpr size_t L2_GROUP_BYTES = (size_t)64 << 20;
+
+inline int l2_group_size(Index batch, size_t bytes_per_entry)
+{
+    size_t budget = L2_GROUP_BYTES;
+#ifdef NB200_EXP_ENV
+    if(const char *e = getenv("NB200_L2_GROUP_MB")) budget = (size_t)atoi(e) << 20;
+#endif
+    const size_t g = budget/(bytes_per_entry > 0 ? bytes_per_entry : 1);
+    return (int)(g < 1 ? 1 : (g > (size_t)batch ? (size_t)batch : g));
+}
+
+__device__ __forceinline__ void group_decode(unsigned cta, int nunits, int batch, int gsz,
+        int &unit, int &b)
+{
+    const unsigned per = (unsigned)gsz*(unsigned)nunits;
+    const unsigned g = cta/per, rem = cta - g*per;
+    const int left = batch - (int)g*gsz;
+    const unsigned cur = (unsigned)(left < gsz ? left : gsz);
+    unit = (int)(rem/cur);
+    b = (int)g*gsz + (int)(rem - (unsigned)unit*cur);
+}
+
 // Classify every block of `mask` into scratch + CLS_OFFSET and clear the status
 // word (flash_fwd_sm100.cu).
 int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *scratch);

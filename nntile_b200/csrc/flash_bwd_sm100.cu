@@ -42,12 +42,12 @@ namespace bwd {
 
 // Optional cycle accounting of the roles (build with -DNB200_PROF).
 #ifdef NB200_PROF
-__device__ unsigned long long g_prof[24];
+__device__ unsigned long long g_prof[32];
 #define PROF_T(var) const long long var = clock64()
-#define PROF_DECL unsigned long long prof_loc[24]; for(int i_ = 0; i_ < 24; ++i_) prof_loc[i_] = 0
+#define PROF_DECL unsigned long long prof_loc[32]; for(int i_ = 0; i_ < 32; ++i_) prof_loc[i_] = 0
 #define PROF_ADD(slot, a, b) prof_loc[slot] += (unsigned long long)((b) - (a))
 #define PROF_INC(slot) prof_loc[slot] += 1ull
-#define PROF_FLUSH for(int i_ = 0; i_ < 24; ++i_) if(prof_loc[i_]) atomicAdd(&g_prof[i_], prof_loc[i_])
+#define PROF_FLUSH for(int i_ = 0; i_ < 32; ++i_) if(prof_loc[i_]) atomicAdd(&g_prof[i_], prof_loc[i_])
 #else
 #define PROF_T(var)
 #define PROF_DECL
@@ -228,7 +228,7 @@ template<int D>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
-        const __grid_constant__ CUtensorMap tmap_g, int seq, int batch, float scale_log2,
+        const __grid_constant__ CUtensorMap tmap_g, int seq, int batch, int gsz, float scale_log2,
         float scale, const bf16 *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
         const float *__restrict__ delta, const float *__restrict__ lse2,
         float *__restrict__ acc_lo, float *__restrict__ acc_hi, Index half_rows,
@@ -254,11 +254,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     Smem<D> &sm = *reinterpret_cast<Smem<D> *>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nblk = seq/BLK;
-    const int kb = (int)(blockIdx.x/batch);      // early key blocks see most queries: first
-    const int b = (int)(blockIdx.x % batch);
+    int kb, b;                                   // early key blocks see most queries: first
+    group_decode(blockIdx.x, nblk, batch, gsz, kb, b);
     const int row_base = b*seq;
     volatile uint32_t *abort_flag = &sm.abort_flag;
     PROF_DECL;
+    PROF_T(c0);
 
     if(tid == 0)
     {
@@ -312,6 +313,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
     const int nact = sm.abort_flag != 0u ? 0 : sm.nact;
+    PROF_T(c1);
     constexpr uint32_t TILE_BYTES = Smem<D>::TILE_BYTES;
     const uint32_t st_tm = tmem, dpt_tm = tmem + 128, dv_tm = tmem + 256, dk_tm = tmem + 256 + D;
     const uint32_t dq_tm = ALIAS ? tmem + 128 : tmem + 384;
@@ -440,9 +442,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     s_pending = false;
                 }
                 PROF_T(m2);
+#ifdef NB200_PROF
+                const bool steady = n >= 2 && n + 2 < nact;
+                if(steady)
+                {
                 PROF_ADD(0, m0, m1);        // MMA: wait for dS^T
                 PROF_ADD(1, m1, m2);        // MMA: issue dK, dQ
                 PROF_INC(7);
+                }
+#endif
                 if(n + 1 >= nact)
                 {
                     tc_commit(&sm.acc_full);
@@ -497,11 +505,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     }
                 }
                 PROF_T(m8);
+#ifdef NB200_PROF
+                if(steady)
+                {
                 PROF_ADD(2, m3, m4);        // MMA: wait for P^T(n+1)
                 PROF_ADD(3, m4, m5);        // MMA: issue dV
                 PROF_ADD(4, m5, m6);        // MMA: wait for the dQ drain
                 PROF_ADD(5, m6, m7);        // MMA: issue dP^T
                 PROF_ADD(6, m7, m8);        // MMA: wait Q + issue S^T(n+2)
+                PROF_ADD(11, m2, m3);       // MMA: wait for dO(n+1)
+                }
+#endif
             }
             if(!ok)
             {
@@ -581,7 +595,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 }
             }
 #ifdef NB200_PROF
-            if(r == 0)
+            if(r == 0 && n >= 2 && n + 2 < nact)
             {
                 PROF_T(d2);
                 PROF_ADD(8, d0, d1);        // drain: wait for dQ
@@ -603,6 +617,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const int h = ts >> 7;                        // query-column half
         const int r = 32*(warp & 3) + lane;           // key row inside the block
         const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
+        if(nact > 0)
+        {
+            // the epilogue adds into this thread's dV (h = 0) or dK (h = 1) row: have
+            // the old values in L2 by then
+            const bf16 *old = (h == 0 ? dV : dK) + ((Index)row_base + (Index)kb*BLK + r)*D;
+#pragma unroll
+            for(int i = 0; i < D/64; ++i)
+            {
+                prefetch_l2(old + 64*i);
+            }
+        }
         bool ok = true;
         int n = 0;
         for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
@@ -614,6 +639,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
             // -lse*log2e and -delta of the query block arrive with the Q tile (bulk
             // copies on the same barrier); this thread handles 64 of the 128 queries
+            PROF_T(sq);
             ok = mbar_wait(&sm.q_full[n & 1], (uint32_t)(n >> 1) & 1u, abort_flag);
             if(!ok) break;
             const float4 *nl4 = reinterpret_cast<const float4 *>(&sm.stats[n & 1][0][64*h]);
@@ -700,6 +726,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             tmem_ld32(dpt_tm + lane_sel + 64*h, dp2[0]);
             tmem_ld32(dpt_tm + lane_sel + 64*h + 32, dp2[1]);
             tmem_ld_wait();
+            PROF_T(b0);
 #pragma unroll
             for(int c2 = 0; c2 < 2; ++c2)
             {
@@ -734,33 +761,47 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                             make_uint4(pd[4*i], pd[4*i + 1], pd[4*i + 2], pd[4*i + 3]);
                 }
             }
+            PROF_T(b1);
             tmem_st_wait();
             fence_proxy_async();
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_full);
 #ifdef NB200_PROF
-            if(ts == 0)
+            if(ts == 0 && n >= 2 && n + 2 < nact)
             {
                 PROF_T(s4);
+                PROF_ADD(22, sq, s0);       // softmax: wait for Q(n) and its statistics
                 PROF_ADD(12, s0, s1);       // softmax: wait for S^T
                 PROF_ADD(13, s1, s2);       // softmax: phase A
                 PROF_ADD(14, s2, s3);       // softmax: wait for dP^T
                 PROF_ADD(16, s3, s4);       // softmax: phase B
+                PROF_ADD(23, s3, b0);       //   of which TMEM load of dP^T
+                PROF_ADD(24, b0, b1);       //   arithmetic, TMEM and shared-memory stores
+                PROF_ADD(25, b1, s4);       //   store wait, fences, arrive
                 PROF_INC(15);
             }
 #endif
             ++n;
         }
         // ---- epilogue: dV (half 0) / dK (half 1) += accumulators ------------------
+        // Each warp owns 32 key rows of dV (h = 0) or dK (h = 1).  TMEM hands a
+        // thread one row, global memory wants a warp on consecutive bytes (one row
+        // per lane costs 32 L1 wavefronts per instruction), so the rounded gradient
+        // goes through a warp-private staging area in the Q/dO stages, which no
+        // MMA or copy touches any more, with rows padded to 272 bytes so that both
+        // the row-per-lane writes and the row-major reads are conflict-free.
+        PROF_T(e0);
         if(ok && nact > 0)
         {
             ok = mbar_wait(&sm.acc_full, 0, abort_flag);
         }
+        PROF_T(e1);
         if(ok && nact > 0)
         {
             tc_fence_after_sync();
-            const Index R = (Index)row_base + (Index)kb*BLK + r;
-            uint4 *orow = reinterpret_cast<uint4 *>((h == 0 ? dV : dK) + R*D);
+            constexpr int PITCH = D*2 + 16;
+            static_assert(8*32*PITCH <= 4*Smem<D>::TILE_BYTES, "staging area");
+            uint8_t *stage = sm.q[0] + (warp - 8)*(32*PITCH);
             const uint32_t src = (h == 0 ? dv_tm : dk_tm) + lane_sel;
             const float mult = h == 0 ? 1.0f : scale;
 #pragma unroll
@@ -772,20 +813,52 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll
                 for(int g4 = 0; g4 < 4; ++g4)
                 {
-                    const uint4 prev = orow[4*cc + g4];
-                    const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
-                    uint32_t outw[4];
+                    uint32_t w[4];
 #pragma unroll
                     for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        const float a0 = __bfloat162float(__float2bfloat16_rn(
-                                __uint_as_float(o[8*g4 + 2*e2])*mult));
-                        const float a1 = __bfloat162float(__float2bfloat16_rn(
-                                __uint_as_float(o[8*g4 + 2*e2 + 1])*mult));
-                        outw[e2] = pack_bf16x2(__uint_as_float(pw[e2] << 16) + a0,
-                                __uint_as_float(pw[e2] & 0xFFFF0000u) + a1);
+                        w[e2] = pack_bf16x2(__uint_as_float(o[8*g4 + 2*e2])*mult,
+                                __uint_as_float(o[8*g4 + 2*e2 + 1])*mult);
                     }
-                    orow[4*cc + g4] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                    *reinterpret_cast<uint4 *>(stage + lane*PITCH + cc*64 + g4*16) =
+                            make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            __syncwarp();
+            constexpr int LPR = D/8;                  // lanes (16-byte pieces) per row
+            constexpr int RPI = 32/LPR;               // rows per warp instruction
+            const int sub = lane/LPR, piece = lane % LPR;
+            bf16 *out = (h == 0 ? dV : dK)
+                    + ((Index)row_base + (Index)kb*BLK + 32*(warp & 3))*D;
+#pragma unroll
+            for(int base = 0; base < 32; base += 8*RPI)
+            {
+                uint4 old[8];
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+                {
+                    const int row = base + j*RPI + sub;
+                    old[j] = *reinterpret_cast<const uint4 *>(out + (Index)row*D + 8*piece);
+                }
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+                {
+                    const int row = base + j*RPI + sub;
+                    const uint4 g = *reinterpret_cast<const uint4 *>(
+                            stage + row*PITCH + 16*piece);
+                    const uint32_t ow[4] = {old[j].x, old[j].y, old[j].z, old[j].w};
+                    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+                    uint32_t r4[4];
+#pragma unroll
+                    for(int e2 = 0; e2 < 4; ++e2)
+                    {
+                        r4[e2] = pack_bf16x2(
+                                __uint_as_float(ow[e2] << 16) + __uint_as_float(gw[e2] << 16),
+                                __uint_as_float(ow[e2] & 0xFFFF0000u)
+                                        + __uint_as_float(gw[e2] & 0xFFFF0000u));
+                    }
+                    *reinterpret_cast<uint4 *>(out + (Index)row*D + 8*piece) =
+                            make_uint4(r4[0], r4[1], r4[2], r4[3]);
                 }
             }
         }
@@ -793,6 +866,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         {
             atomicExch(status, 14u);
         }
+#ifdef NB200_PROF
+        if(ts == 0)
+        {
+            PROF_T(e2);
+            PROF_ADD(19, e0, e1);           // epilogue: wait for the last MMAs
+            PROF_ADD(20, e1, e2);           // epilogue: read-modify-write of dK, dV
+            PROF_ADD(17, c0, e2);           // CTA lifetime seen by a softmax thread
+            PROF_ADD(18, c0, c1);           // prologue up to the first __syncthreads
+            PROF_INC(21);
+        }
+#endif
     }
     // ---- tear-down ---------------------------------------------------------------
     PROF_FLUSH;
@@ -814,13 +898,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 } // namespace bwd
 
 #ifdef NB200_PROF
-extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out24, int reset)
+extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out32, int reset)
 {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out24, bwd::g_prof, sizeof(unsigned long long)*24);
+    cudaMemcpyFromSymbol(out32, bwd::g_prof, sizeof(unsigned long long)*32);
     if(reset)
     {
-        unsigned long long z[24] = {0};
+        unsigned long long z[32] = {0};
         cudaMemcpyToSymbol(bwd::g_prof, z, sizeof(z));
     }
 }
@@ -884,8 +968,10 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
         return NNTILE_B200_E_LAUNCH;
     }
     const float scale = 1.0f/sqrtf((float)D);
+    // Q, K, V, dO, dK, dV (bf16) and the fp32 dQ accumulator of one batch entry
+    const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
     flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg,
-            (int)seq, (int)batch, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
+            (int)seq, (int)batch, gsz, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
             acc_lo, acc_hi, half_rows, dK, dV, reinterpret_cast<uint32_t *>(sc));
     if(launch_status() != NNTILE_B200_OK)
     {

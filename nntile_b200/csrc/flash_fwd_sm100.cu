@@ -192,7 +192,7 @@ template<int D>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-        int seq, int batch, float scale_log2, const bf16 *__restrict__ mask,
+        int seq, int batch, int gsz, float scale_log2, const bf16 *__restrict__ mask,
         uint8_t *scratch, float *__restrict__ lse, bf16 *__restrict__ A)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -201,8 +201,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nblk = seq/BLK;
     const int npairs = (nblk + 1)/2;
-    const int pair = npairs - 1 - (int)(blockIdx.x/batch);     // heavy (late) rows first
-    const int b = (int)(blockIdx.x % batch);
+    int unit, b;
+    group_decode(blockIdx.x, npairs, batch, gsz, unit, b);
+    const int pair = npairs - 1 - unit;                         // heavy (late) rows first
     const int qb0 = 2*pair, qb1 = 2*pair + 1;
     const bool has1 = qb1 < nblk;
     const uint8_t *cls_tab = scratch + CLS_OFFSET;
@@ -743,7 +744,9 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     }
     const unsigned grid = (unsigned)(((nblk + 1)/2)*batch);
     const float scale_log2 = LOG2E_F/sqrtf((float)D);
-    flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, (int)seq, (int)batch,
+    // Q, K, V, A of one batch entry
+    const int gsz = l2_group_size(batch, (size_t)seq*D*2*4);
+    flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, (int)seq, (int)batch, gsz,
             scale_log2, mask, scratch, lse, A);
     return launch_status();
 }

@@ -133,6 +133,11 @@ __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_sr
            "r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void prefetch_l2(const void *p)
+{
+    asm volatile("prefetch.global.L2 [%0];" :: "l"(p) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map)
 {
     asm volatile("prefetch.tensormap [%0];" :: "l"(reinterpret_cast<uint64_t>(map)) : "memory");
