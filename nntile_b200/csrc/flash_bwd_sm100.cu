@@ -795,6 +795,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         {
             ok = mbar_wait(&sm.acc_full, 0, abort_flag);
         }
+        ok = __all_sync(0xffffffffu, ok);     // the epilogue is warp-collective
         PROF_T(e1);
         if(ok && nact > 0)
         {

@@ -607,6 +607,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         {
             ok = mbar_wait(&sm.o_full[t], 0, abort_flag);
         }
+        ok = __all_sync(0xffffffffu, ok);     // the epilogue is warp-collective
         if(ok && nact > 0)
         {
             tc_fence_after_sync();
@@ -637,39 +638,80 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 lse[R] = big + logf(1.0f + e);
             }
             const float inv = live ? 1.0f/l : 0.0f;
-            uint4 *arow = reinterpret_cast<uint4 *>(A + R*D);
+            // TMEM hands a thread one row, global memory wants a warp on consecutive
+            // bytes (one row per lane costs 32 L1 wavefronts per instruction): the
+            // normalised tile result, rounded to storage as the reference's scratch
+            // output is, goes through this warp's 32 rows of the Q tile, which no MMA
+            // reads any more; 16-byte pieces are XOR-swizzled with the row so that the
+            // row-per-lane writes and the row-major reads are both conflict-free.
+            constexpr int PITCH = D*2;
+            uint8_t *stage = sm.q[t] + (warp & 3)*(32*PITCH);
 #pragma unroll
             for(int cc = 0; cc < D/32; ++cc)
             {
                 uint32_t o[32];
                 tmem_ld32(o_tm + 32*cc, o);
                 tmem_ld_wait();
-                if(live)
+#pragma unroll
+                for(int g = 0; g < 4; ++g)
                 {
+                    uint32_t w[4];
 #pragma unroll
-                    for(int g = 0; g < 4; ++g)
+                    for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        uint4 prev = make_uint4(0u, 0u, 0u, 0u);
-                        if(w_dst != 0.0f)      // a weight of zero never reads the old row
-                        {
-                            prev = arow[4*cc + g];
-                        }
-                        const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
-                        uint32_t outw[4];
+                        w[e2] = pack_bf16x2(__uint_as_float(o[8*g + 2*e2])*inv,
+                                __uint_as_float(o[8*g + 2*e2 + 1])*inv);
+                    }
+                    *reinterpret_cast<uint4 *>(stage + lane*PITCH + (((4*cc + g) ^ (lane & 7)) << 4)) =
+                            make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            __syncwarp();
+            constexpr int LPR = D/8;                  // lanes (16-byte pieces) per row
+            constexpr int RPI = 32/LPR;               // rows per warp instruction
+            const int sub = lane/LPR, piece = lane % LPR;
+            bf16 *out = A + ((size_t)row_base + (size_t)qb*BLK + 32*(warp & 3))*D;
 #pragma unroll
-                        for(int e2 = 0; e2 < 4; ++e2)
-                        {
-                            // the tile result is rounded to storage before the merge,
-                            // as the reference's scratch output is
-                            const float a0 = __bfloat162float(__float2bfloat16_rn(
-                                    __uint_as_float(o[8*g + 2*e2])*inv));
-                            const float a1 = __bfloat162float(__float2bfloat16_rn(
-                                    __uint_as_float(o[8*g + 2*e2 + 1])*inv));
-                            const float p0 = __uint_as_float(pw[e2] << 16);
-                            const float p1 = __uint_as_float(pw[e2] & 0xFFFF0000u);
-                            outw[e2] = pack_bf16x2(w_dst*p0 + w_src*a0, w_dst*p1 + w_src*a1);
-                        }
-                        arow[4*cc + g] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+            for(int base = 0; base < 32; base += 8*RPI)
+            {
+                uint4 prev[8];
+                float wd[8], ws[8];
+                bool lv[8];
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+                {
+                    const int row = base + j*RPI + sub;
+                    wd[j] = __shfl_sync(0xffffffffu, w_dst, row);
+                    ws[j] = __shfl_sync(0xffffffffu, w_src, row);
+                    lv[j] = __shfl_sync(0xffffffffu, (int)live, row) != 0;
+                    prev[j] = make_uint4(0u, 0u, 0u, 0u);
+                    if(lv[j] && wd[j] != 0.0f)        // a weight of zero never reads the old row
+                    {
+                        prev[j] = *reinterpret_cast<const uint4 *>(out + (size_t)row*D + 8*piece);
+                    }
+                }
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+                {
+                    const int row = base + j*RPI + sub;
+                    const uint4 g = *reinterpret_cast<const uint4 *>(
+                            stage + row*PITCH + ((piece ^ (row & 7)) << 4));
+                    const uint32_t pw[4] = {prev[j].x, prev[j].y, prev[j].z, prev[j].w};
+                    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+                    uint32_t outw[4];
+#pragma unroll
+                    for(int e2 = 0; e2 < 4; ++e2)
+                    {
+                        outw[e2] = pack_bf16x2(
+                                wd[j]*__uint_as_float(pw[e2] << 16)
+                                        + ws[j]*__uint_as_float(gw[e2] << 16),
+                                wd[j]*__uint_as_float(pw[e2] & 0xFFFF0000u)
+                                        + ws[j]*__uint_as_float(gw[e2] & 0xFFFF0000u));
+                    }
+                    if(lv[j])
+                    {
+                        *reinterpret_cast<uint4 *>(out + (size_t)row*D + 8*piece) =
+                                make_uint4(outw[0], outw[1], outw[2], outw[3]);
                     }
                 }
             }
