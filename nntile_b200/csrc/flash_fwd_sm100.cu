@@ -284,8 +284,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // control warpgroup: give registers away, then producer / MMA issuer / idle.
     // An increase is only ever served from registers a warpgroup of this CTA gave
     // up, and waits for them without a bound, so released must equal requested:
-    // launch 168 x 384 = control 56 x 128 + softmax 224 x 256.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    // launch 168 x 384 = control 72 x 128 + softmax 216 x 256 (at 56 the
+    // issuing thread spills and at 208 the softmax rows do; both cost several percent).
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if(warp == 0)
     {
         // =============================== TMA producer ==========================
@@ -400,13 +401,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if(!ok) break;
                     tc_fence_after_sync();
                     PROF_T(mt1);
-                    issue_pv<D, 0>(o_tm[t], s_tm[t], v_lo[st], n_pv[t] > 0);
                     PROF_T(mt2);
                     ok = mbar_wait(&sm.p_half[t][1], p_phase[t], abort_flag);
                     if(!ok) break;
                     p_phase[t] ^= 1u;
                     tc_fence_after_sync();
                     PROF_T(mt3);
+                    issue_pv<D, 0>(o_tm[t], s_tm[t], v_lo[st], n_pv[t] > 0);
                     issue_pv<D, 1>(o_tm[t], s_tm[t], v_lo[st], true);
                     PROF_T(mt4);
                     PROF_ADD(8, mt0, mt1);      // MMA thread: wait for first half of P
@@ -440,7 +441,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
     else
     {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ============================= softmax groups ==========================
         const int t = (warp - 4) >> 2;                    // query tile of this group
         const int r = 32*(warp & 3) + lane;               // row inside the tile
