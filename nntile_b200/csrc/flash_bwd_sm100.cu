@@ -9,20 +9,29 @@
 //
 // One CTA owns one block of 128 keys of one batch entry: K and V stay in shared
 // memory, dK and dV stay in TMEM for the whole loop over the query blocks that
-// see these keys.  Everything is computed transposed (rows = keys) so that the
-// probabilities land in TMEM exactly where the next MMA wants its A operand:
+// see these keys.  Everything is computed transposed (rows = keys):
 //   S^T  = K Q^T          (shared x shared, both K-major)
 //   dP^T = V dO^T         (shared x shared)
 //   P^T  = exp2(S^T*c - lse2), dS^T = P^T o (dP^T - delta)      softmax warps
-//   dV  += P^T dO         (P^T from TMEM, dO MN-major from shared memory)
-//   dK  += dS^T Q         (dS^T from TMEM, Q MN-major)
-//   dQ_i = dS K           (dS^T written to shared memory by the softmax warps,
-//                          read as an MN-major A operand; K MN-major)
-// dQ_i is added into an fp32 accumulator in global memory with vector red.add
-// (several key blocks contribute to a query row), converted and added into dQ by
-// a small epilogue kernel.  TMEM: S^T 128 + dP^T 128 + dV D + dK D columns; for
-// head 128 that is all 512, so dQ_i reuses the dP^T columns once dK has consumed
-// dS^T (the MMA pipe runs in issue order) and the next dP^T waits for the drain.
+//   dV  += P^T dO         (P^T from TMEM, where the softmax warps wrote it over
+//                          S^T; dO MN-major from shared memory)
+//   dK  += dS^T Q         (dS^T from TMEM, written over dP^T; Q MN-major)
+//   dQ_i = dS K           (dS^T also written to shared memory by the softmax warps,
+//                          read as an MN-major operand; K MN-major)
+// dQ_i is added into an fp32 accumulator in global memory with red.add (several
+// key blocks contribute to a query row), converted and added into dQ by a small
+// epilogue kernel.  TMEM: S^T 128 + dP^T 128 + dV D + dK D columns; for head 128
+// that is all 512, so dQ_i reuses the dP^T columns once dK has consumed dS^T (the
+// MMA pipe runs in issue order) and the next dP^T waits for the drain warps to
+// read dQ_i out.  (Reading dS^T for dK from shared memory instead, so that dQ_i
+// could go first, was slower: with both operands of four of the five products in
+// shared memory its 128 bytes per clock are the busiest resource of the SM.)
+//
+// The chip's L2 takes about 21 bytes of fp32 reductions per clock and SM; a
+// drain warp that issues its 128 reductions back to back fills the load/store
+// queue for 3000 clocks and every shared-memory and TMEM access of the softmax
+// warps waits behind them, so the drain issues four at a time on a clock schedule
+// just below that rate.
 //
 // 512 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 dQ drain,
 // warps 8-15 softmax (two warps per TMEM lane quarter, 64 query columns each).
@@ -58,6 +67,13 @@ __device__ unsigned long long g_prof[32];
 
 constexpr int BLK = 128;
 constexpr int THREADS = 512;
+#ifndef NB200_RED_PACE
+#define NB200_RED_PACE 24
+#endif
+#ifndef NB200_RED_BURST
+#define NB200_RED_BURST 4
+#endif
+constexpr int RED_PACE = NB200_RED_PACE, RED_BURST = NB200_RED_BURST;
 constexpr int MAX_BLOCKS = 256;      // seq <= 32768
 constexpr float LOG2E_F = 1.4426950408889634f;
 
@@ -557,6 +573,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 mbar_arrive(&sm.dq_empty);
+                const long long red_t0 = clock64();
 #pragma unroll
                 for(int cc = 0; cc < BLK/32; ++cc)
                 {
@@ -567,6 +584,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     for(int j = 0; j < 32; ++j)
                     {
                         red_add_f32(dst + (Index)j*D, __uint_as_float(o[cc][j]));
+                        if((j % RED_BURST) == RED_BURST - 1)
+                        {
+                            // stay behind the schedule of one reduction per RED_PACE clocks
+                            const long long due = red_t0 + (long long)(32*cc + j + 1)*RED_PACE;
+                            while(clock64() < due)
+                            {
+                                __nanosleep(20);
+                            }
+                        }
                     }
                 }
             }
