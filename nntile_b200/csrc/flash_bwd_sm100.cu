@@ -98,25 +98,46 @@ struct Smem
 
 // delta[r] = -sum_h A[r,h]*dA[r,h];  lse2[r] = -lse[r]*log2(e)  (both are only ever
 // used negated by the main kernel)
-__global__ void bwd_prep_kernel(int head, Index rows, const bf16 *__restrict__ A,
+// Also clears the fp32 dQ accumulator (split at half_rows over two buffers).  head/8
+// threads per row, 16 bytes of A and of dA per thread; head is 64 or 128.
+__global__ void __launch_bounds__(256)
+bwd_prep_kernel(int head, Index rows, Index half_rows, const bf16 *__restrict__ A,
         const bf16 *__restrict__ dA, const float *__restrict__ lse,
-        float *__restrict__ delta, float *__restrict__ lse2)
+        float *__restrict__ delta, float *__restrict__ lse2, float *__restrict__ acc_lo,
+        float *__restrict__ acc_hi)
 {
-    const int lane = threadIdx.x & 31;
-    const Index r = (Index)blockIdx.x*(blockDim.x >> 5) + (threadIdx.x >> 5);
-    if(r >= rows)
-    {
-        return;
-    }
+    const int tpr = head >> 3;                            // threads per row: 8 or 16
+    const Index idx = (Index)blockIdx.x*blockDim.x + threadIdx.x;
+    const Index r = idx/tpr;
+    const int piece = (int)(idx - r*tpr);
     float acc = 0.0f;
-    for(int h = 2*lane; h < head; h += 64)
+    if(r < rows)
     {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(A + r*head + h));
-        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(dA + r*head + h));
-        acc = fmaf(a.x, g.x, fmaf(a.y, g.y, acc));
+        const uint4 a = *reinterpret_cast<const uint4 *>(A + r*head + 8*piece);
+        const uint4 g = *reinterpret_cast<const uint4 *>(dA + r*head + 8*piece);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for(int e = 0; e < 4; ++e)
+        {
+            acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), acc);
+            acc = fmaf(__uint_as_float(aw[e] & 0xFFFF0000u), __uint_as_float(gw[e] & 0xFFFF0000u),
+                    acc);
+        }
+        float4 *z = reinterpret_cast<float4 *>(
+                (r < half_rows ? acc_lo + r*head : acc_hi + (r - half_rows)*head) + 8*piece);
+        z[0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        z[1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
-    acc = warp_sum(acc);
-    if(lane == 0)
+    // rows never straddle a warp: 32 is a multiple of tpr and blockDim of 32
+#pragma unroll
+    for(int off = 8; off >= 1; off >>= 1)
+    {
+        if(off < tpr)
+        {
+            acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        }
+    }
+    if(r < rows && piece == 0)
     {
         delta[r] = -acc;
         lse2[r] = -lse[r]*LOG2E_F;
@@ -964,18 +985,13 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     float *lse2 = delta + rows;
     float *acc_lo = static_cast<float *>(scratch_dQ), *acc_hi = static_cast<float *>(scratch_dK);
     const Index half_rows = rows/2;
-    const size_t half_bytes = (size_t)rows*D*2;
-    if(cudaMemsetAsync(acc_lo, 0, half_bytes, s) != cudaSuccess
-            || cudaMemsetAsync(acc_hi, 0, half_bytes, s) != cudaSuccess)
-    {
-        return NNTILE_B200_E_LAUNCH;
-    }
     int st = launch_mask_classify(s, (int)seq, mask, sc);
     if(st != NNTILE_B200_OK)
     {
         return st;
     }
-    bwd_prep_kernel<<<(unsigned)((rows + 7)/8), 256, 0, s>>>(D, rows, A, dA, lse, delta, lse2);
+    bwd_prep_kernel<<<(unsigned)((rows*(D/8) + 255)/256), 256, 0, s>>>(D, rows, half_rows, A, dA,
+            lse, delta, lse2, acc_lo, acc_hi);
     if(launch_status() != NNTILE_B200_OK)
     {
         return NNTILE_B200_E_LAUNCH;
