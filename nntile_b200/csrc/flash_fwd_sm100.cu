@@ -335,10 +335,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // unused; MN-major V: next 64 head columns one 16 KB panel away)
             const uint32_t q_lo[2] = {smem_desc_lo(smem_u32(sm.q[0]), 16),
                                       smem_desc_lo(smem_u32(sm.q[1]), 16)};
-            const uint32_t k_lo[KV_STAGES] = {smem_desc_lo(smem_u32(sm.k[0]), 16),
-                                              smem_desc_lo(smem_u32(sm.k[1]), 16)};
-            const uint32_t v_lo[KV_STAGES] = {smem_desc_lo(smem_u32(sm.v[0]), BLK*128),
-                                              smem_desc_lo(smem_u32(sm.v[1]), BLK*128)};
+            // stage s of K / V: low word of stage 0 + s*STAGE_LO (no indexed local arrays:
+            // everything this thread keeps must stay in registers)
+            const uint32_t k_lo0 = smem_desc_lo(smem_u32(sm.k[0]), 16);
+            const uint32_t v_lo0 = smem_desc_lo(smem_u32(sm.v[0]), BLK*128);
+            constexpr uint32_t STAGE_LO = (uint32_t)(Smem<D>::TILE_BYTES >> 4);
+            const int nact_r[2] = {sm.nact[0], sm.nact[1]};
             int qk_done[2] = {-1, -1};          // last iteration whose QK_t was issued
             int n_pv[2] = {0, 0};               // PV steps issued per tile
             int k_waited = -1, k_released = -1;
@@ -346,12 +348,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
             for(int t = 0; t < 2; ++t)
             {
-                if(sm.nact[t] > 0)
+                if(nact_r[t] > 0)
                 {
                     ok = mbar_wait(&sm.q_full[t], 0, abort_flag);
                 }
             }
-            auto qk = [&](int t, int it) -> bool
+            // cls_other: class of the same block for the other tile
+            auto qk = [&](int t, int it, uint8_t cls_other) -> bool
             {
                 const int st = it % KV_STAGES;
                 if(it > k_waited)
@@ -363,36 +366,45 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     k_waited = it;
                     tc_fence_after_sync();
                 }
-                issue_qk<D>(s_tm[t], q_lo[t], k_lo[st]);
+                issue_qk<D>(s_tm[t], q_lo[t], k_lo0 + (uint32_t)st*STAGE_LO);
                 tc_commit(&sm.s_full[t]);
                 qk_done[t] = it;
                 // release the K stage once every tile that needs this block has issued
                 const int o = t ^ 1;
-                if(it > k_released && (sm.cls[o][it] == CLS_SKIP || qk_done[o] >= it))
+                if(it > k_released && (cls_other == CLS_SKIP || qk_done[o] >= it))
                 {
                     tc_commit(&sm.k_empty[st]);
                     k_released = it;
                 }
                 return true;
             };
+            // classes of the current and the next block, read once per block
+            uint8_t cur[2] = {sm.cls[0][0], sm.cls[1][0]};
             for(int it = 0; it < nproc && ok; ++it)
             {
                 const int st = it % KV_STAGES;
+                uint8_t nxt[2] = {CLS_SKIP, CLS_SKIP};
+                if(it + 1 < nproc)
+                {
+                    nxt[0] = sm.cls[0][it + 1];
+                    nxt[1] = sm.cls[1][it + 1];
+                }
     #pragma unroll
             for(int t = 0; t < 2; ++t)
                 {
-                    if(sm.cls[t][it] != CLS_SKIP && qk_done[t] < it)
+                    if(cur[t] != CLS_SKIP && qk_done[t] < it)
                     {
-                        ok = qk(t, it);
+                        ok = qk(t, it, cur[t ^ 1]);
                     }
                 }
                 if(!ok) break;
                 ok = mbar_wait(&sm.v_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag);
-                const int last_t = sm.cls[1][it] != CLS_SKIP ? 1 : 0;
+                const int last_t = cur[1] != CLS_SKIP ? 1 : 0;
+                const uint32_t v_lo = v_lo0 + (uint32_t)st*STAGE_LO;
     #pragma unroll
             for(int t = 0; t < 2; ++t)
                 {
-                    if(sm.cls[t][it] == CLS_SKIP)
+                    if(cur[t] == CLS_SKIP)
                     {
                         continue;
                     }
@@ -407,8 +419,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     p_phase[t] ^= 1u;
                     tc_fence_after_sync();
                     PROF_T(mt3);
-                    issue_pv<D, 0>(o_tm[t], s_tm[t], v_lo[st], n_pv[t] > 0);
-                    issue_pv<D, 1>(o_tm[t], s_tm[t], v_lo[st], true);
+                    issue_pv<D, 0>(o_tm[t], s_tm[t], v_lo, n_pv[t] > 0);
+                    issue_pv<D, 1>(o_tm[t], s_tm[t], v_lo, true);
                     PROF_T(mt4);
                     PROF_ADD(8, mt0, mt1);      // MMA thread: wait for first half of P
                     PROF_ADD(9, mt1, mt2);      // issue 4 PV steps
@@ -422,15 +434,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     {
                         tc_commit(&sm.v_empty[st]);
                     }
-                    if(n_pv[t] == sm.nact[t])
+                    if(n_pv[t] == nact_r[t])
                     {
                         tc_commit(&sm.o_full[t]);
                     }
-                    else if(it + 1 < nproc && sm.cls[t][it + 1] != CLS_SKIP)
+                    else if(nxt[t] != CLS_SKIP)
                     {
-                        ok = qk(t, it + 1);
+                        ok = qk(t, it + 1, nxt[t ^ 1]);
                     }
                 }
+                cur[0] = nxt[0];
+                cur[1] = nxt[1];
             }
             if(!ok)
             {
