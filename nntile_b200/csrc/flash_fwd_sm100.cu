@@ -111,7 +111,7 @@ struct Smem
     uint64_t q_full[2];
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-    uint64_t s_full[2], p_half[2][2], o_full[2];
+    uint64_t s_full[2], p_full[2], o_full[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
     int nproc;
@@ -216,8 +216,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         {
             mbar_init(&sm.q_full[i], 1);
             mbar_init(&sm.s_full[i], 1);
-            mbar_init(&sm.p_half[i][0], 128);
-            mbar_init(&sm.p_half[i][1], 128);
+            mbar_init(&sm.p_full[i], 128);
             mbar_init(&sm.o_full[i], 1);
         }
         for(int i = 0; i < KV_STAGES; ++i)
@@ -409,12 +408,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         continue;
                     }
                     PROF_T(mt0);
-                    ok = mbar_wait(&sm.p_half[t][0], p_phase[t], abort_flag);
-                    if(!ok) break;
-                    tc_fence_after_sync();
                     PROF_T(mt1);
                     PROF_T(mt2);
-                    ok = mbar_wait(&sm.p_half[t][1], p_phase[t], abort_flag);
+                    ok = mbar_wait(&sm.p_full[t], p_phase[t], abort_flag);
                     if(!ok) break;
                     p_phase[t] ^= 1u;
                     tc_fence_after_sync();
@@ -422,9 +418,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     issue_pv<D, 0>(o_tm[t], s_tm[t], v_lo, n_pv[t] > 0);
                     issue_pv<D, 1>(o_tm[t], s_tm[t], v_lo, true);
                     PROF_T(mt4);
-                    PROF_ADD(8, mt0, mt1);      // MMA thread: wait for first half of P
+                    PROF_ADD(8, mt0, mt1);      // (unused)
                     PROF_ADD(9, mt1, mt2);      // issue 4 PV steps
-                    PROF_ADD(10, mt2, mt3);     // wait for second half of P
+                    PROF_ADD(10, mt2, mt3);     // MMA thread: wait for P
                     PROF_ADD(11, mt3, mt4);     // issue 4 PV steps
 #ifdef NB200_PROF
                     atomicAdd(&g_prof[12], 1ull);
@@ -568,8 +564,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             m_used = m_new;
             const float neg_ref = m_used == -CUDART_INF_F ? 0.0f : -m_used;
             PROF_T(pt4);
-            // ---- P = exp2(x - m), row sum, bf16 pack, back into the S columns; the
-            // two halves of the row are handed to the MMA warp separately ------------
+            // ---- P = exp2(x - m), row sum, bf16 pack, back into the S columns (in two
+            // rounds of 64 values to bound the registers), then one hand-over ---------
             const uint64_t mul2 = pack_f32x2(mul, mul), ref2 = pack_f32x2(neg_ref, neg_ref);
             uint64_t sum_a = 0ull, sum_b = 0ull;          // two packed chains = four sums
 #pragma unroll
@@ -592,10 +588,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     pk[j + 1] = pack_bf16x2(pb0, pb1);
                 }
                 tmem_st32(s_tm + 32*h, pk);
-                tmem_st_wait();
-                tc_fence_before_sync();
-                mbar_arrive(&sm.p_half[t][h]);
             }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_full[t]);
             {
                 float a0, a1, b0, b1;
                 unpack_f32x2(fadd2(sum_a, sum_b), a0, a1);
