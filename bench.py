@@ -58,9 +58,10 @@ C2 = dict(head=64, seq=1024, batch=8, group=1, kv_heads=12)
 C4 = dict(head=128, seq=16384, batch=1, group=1, kv_heads=16, seq_tile=2048)
 C5 = dict(head=128, max_seq=8192, batch=64, group=4, kv_heads=8)
 # DRAM bytes per (batch, head) slice of head 128, seq 4096 measured with ncu
-# (dram__bytes_read.sum + dram__bytes_write.sum of one launch on 16 slices; traffic
-# is proportional to the number of slices because slices are independent)
-NCU_DRAM_BYTES_PER_SLICE = {"flash_bwd_kernel<128>": 164.2e6/16, "flash_fwd_kernel<128>": 52.7e6/16}
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch, one-pass capture
+# of the full 128-slice workload; slices are independent, so a launch on fewer
+# slices moves proportionally less)
+NCU_DRAM_BYTES_PER_SLICE = {"flash_bwd_kernel<128>": 1579.6e6/128, "flash_fwd_kernel<128>": 532.9e6/128}
 
 
 def causal_flops(cfg):
@@ -408,8 +409,8 @@ def run_gpu_arm(args):
         "frac": achieved/peaks["bf16"], "peak_source": peaks["source"] + " sustained bf16 GEMM",
         "traffic": (NCU_DRAM_BYTES_PER_SLICE["flash_bwd_kernel<128>"]*wl.nb
                     if (cfg["head"], cfg["seq"]) == (128, 4096) and bwd_path == 2 else None),
-        "traffic_note": "DRAM bytes per launch of flash_bwd_kernel<128> from an ncu capture on 16 "
-                        "slices, scaled by the slices of this launch (profiles/)",
+        "traffic_note": "DRAM bytes per launch of flash_bwd_kernel<128> from a one-pass ncu capture "
+                        "of the 128-slice workload, scaled by the slices of this launch (profiles/)",
         "fwd": {"achieved": wl.flops_fwd/(fwd_med*1e-3)/1e12, "ms": fwd_med,
                 "frac": wl.flops_fwd/(fwd_med*1e-3)/1e12/peaks["bf16"]},
         "bwd_ms": bwd_med,
