@@ -265,7 +265,8 @@ template<int D>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
-        const __grid_constant__ CUtensorMap tmap_g, int seq, int batch, int gsz, float scale_log2,
+        const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_dk,
+        const __grid_constant__ CUtensorMap tmap_dv, int seq, int batch, int gsz, float scale_log2,
         float scale, const bf16 *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
         const float *__restrict__ delta, const float *__restrict__ lse2,
         float *__restrict__ acc_lo, float *__restrict__ acc_hi, Index half_rows,
@@ -321,6 +322,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         prefetch_tensormap(&tmap_v);
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_g);
+        prefetch_tensormap(&tmap_dk);
+        prefetch_tensormap(&tmap_dv);
     }
     if(warp == 1)
     {
@@ -664,17 +667,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const int h = ts >> 7;                        // query-column half
         const int r = 32*(warp & 3) + lane;           // key row inside the block
         const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
-        if(nact > 0)
-        {
-            // the epilogue adds into this thread's dV (h = 0) or dK (h = 1) row: have
-            // the old values in L2 by then
-            const bf16 *old = (h == 0 ? dV : dK) + ((Index)row_base + (Index)kb*BLK + r)*D;
-#pragma unroll
-            for(int i = 0; i < D/64; ++i)
-            {
-                prefetch_l2(old + 64*i);
-            }
-        }
         bool ok = true;
         int n = 0;
         for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
@@ -831,25 +823,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             ++n;
         }
         // ---- epilogue: dV (half 0) / dK (half 1) += accumulators ------------------
-        // Each warp owns 32 key rows of dV (h = 0) or dK (h = 1).  TMEM hands a
-        // thread one row, global memory wants a warp on consecutive bytes (one row
-        // per lane costs 32 L1 wavefronts per instruction), so the rounded gradient
-        // goes through a warp-private staging area in the Q/dO stages, which no
-        // MMA or copy touches any more, with rows padded to 272 bytes so that both
-        // the row-per-lane writes and the row-major reads are conflict-free.
+        // Each warp owns 32 key rows of dV (h = 0) or dK (h = 1).  The gradient is
+        // rounded to bf16 and written into the warp's part of the Q stage (dV) or dO
+        // stage (dK) that the LAST query block did not use, as 64-column panels with
+        // 128-byte rows and the 128-byte swizzle of the tensor maps, and one lane
+        // hands the panels to the TMA unit as element-wise bf16 additions into dV /
+        // dK: the reference's "+=" without this SM reading the old values or
+        // waiting for them.  That stage was last touched by the block before the
+        // last one; its hand-back barrier is waited for first.
         PROF_T(e0);
+        const int sf = nact & 1;
         if(ok && nact > 0)
         {
             ok = mbar_wait(&sm.acc_full, 0, abort_flag);
+        }
+        if(ok && nact >= 2)
+        {
+            ok = mbar_wait(h == 0 ? &sm.q_empty[sf] : &sm.g_empty[sf],
+                    (uint32_t)((nact - 2) >> 1) & 1u, abort_flag);
         }
         ok = __all_sync(0xffffffffu, ok);     // the epilogue is warp-collective
         PROF_T(e1);
         if(ok && nact > 0)
         {
             tc_fence_after_sync();
-            constexpr int PITCH = D*2 + 16;
-            static_assert(8*32*PITCH <= 4*Smem<D>::TILE_BYTES, "staging area");
-            uint8_t *stage = sm.q[0] + (warp - 8)*(32*PITCH);
+            constexpr int PANELS = D/64;
+            uint8_t *stage = (h == 0 ? sm.q[sf] : sm.g[sf]) + (warp & 3)*(PANELS*4096);
             const uint32_t src = (h == 0 ? dv_tm : dk_tm) + lane_sel;
             const float mult = h == 0 ? 1.0f : scale;
 #pragma unroll
@@ -858,6 +857,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 uint32_t o[32];
                 tmem_ld32(src + 32*cc, o);
                 tmem_ld_wait();
+                // columns 32cc .. 32cc+31 = pieces 4*(cc & 1) .. +3 of panel cc >> 1
+                uint8_t *prow = stage + (cc >> 1)*4096 + lane*128;
 #pragma unroll
                 for(int g4 = 0; g4 < 4; ++g4)
                 {
@@ -868,46 +869,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         w[e2] = pack_bf16x2(__uint_as_float(o[8*g4 + 2*e2])*mult,
                                 __uint_as_float(o[8*g4 + 2*e2 + 1])*mult);
                     }
-                    *reinterpret_cast<uint4 *>(stage + lane*PITCH + cc*64 + g4*16) =
+                    *reinterpret_cast<uint4 *>(prow + (((4*(cc & 1) + g4) ^ (lane & 7)) << 4)) =
                             make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
+            fence_proxy_async();
             __syncwarp();
-            constexpr int LPR = D/8;                  // lanes (16-byte pieces) per row
-            constexpr int RPI = 32/LPR;               // rows per warp instruction
-            const int sub = lane/LPR, piece = lane % LPR;
-            bf16 *out = (h == 0 ? dV : dK)
-                    + ((Index)row_base + (Index)kb*BLK + 32*(warp & 3))*D;
-#pragma unroll
-            for(int base = 0; base < 32; base += 8*RPI)
+            if(lane == 0)
             {
-                uint4 old[8];
+                const int row0 = row_base + kb*BLK + 32*(warp & 3);
 #pragma unroll
-                for(int j = 0; j < 8; ++j)
+                for(int p = 0; p < PANELS; ++p)
                 {
-                    const int row = base + j*RPI + sub;
-                    old[j] = *reinterpret_cast<const uint4 *>(out + (Index)row*D + 8*piece);
+                    tma_reduce_add_2d(h == 0 ? &tmap_dv : &tmap_dk, stage + p*4096, 64*p, row0);
                 }
-#pragma unroll
-                for(int j = 0; j < 8; ++j)
-                {
-                    const int row = base + j*RPI + sub;
-                    const uint4 g = *reinterpret_cast<const uint4 *>(
-                            stage + row*PITCH + 16*piece);
-                    const uint32_t ow[4] = {old[j].x, old[j].y, old[j].z, old[j].w};
-                    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-                    uint32_t r4[4];
-#pragma unroll
-                    for(int e2 = 0; e2 < 4; ++e2)
-                    {
-                        r4[e2] = pack_bf16x2(
-                                __uint_as_float(ow[e2] << 16) + __uint_as_float(gw[e2] << 16),
-                                __uint_as_float(ow[e2] & 0xFFFF0000u)
-                                        + __uint_as_float(gw[e2] & 0xFFFF0000u));
-                    }
-                    *reinterpret_cast<uint4 *>(out + (Index)row*D + 8*piece) =
-                            make_uint4(r4[0], r4[1], r4[2], r4[3]);
-                }
+                bulk_commit_group();
+                bulk_wait_read_all();
             }
         }
         if(!ok && lane == 0)
@@ -996,10 +973,12 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     {
         return NNTILE_B200_E_LAUNCH;
     }
-    CUtensorMap tk, tv, tq, tg;
+    CUtensorMap tk, tv, tq, tg, tdk, tdv;
     if(!make_tmap_bf16_sw128(&tk, K, rows, D, BLK) || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK)
             || !make_tmap_bf16_sw128(&tq, Q, rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK))
+            || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK)
+            || !make_tmap_bf16_sw128(&tdk, dK, rows, D, 32)
+            || !make_tmap_bf16_sw128(&tdv, dV, rows, D, 32))
     {
         return NNTILE_B200_E_LAUNCH;
     }
@@ -1013,7 +992,7 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     const float scale = 1.0f/sqrtf((float)D);
     // Q, K, V, dO, dK, dV (bf16) and the fp32 dQ accumulator of one batch entry
     const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
-    flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg,
+    flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg, tdk, tdv,
             (int)seq, (int)batch, gsz, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
             acc_lo, acc_hi, half_rows, dK, dV, reinterpret_cast<uint32_t *>(sc));
     if(launch_status() != NNTILE_B200_OK)

@@ -133,6 +133,38 @@ __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_sr
            "r"(smem_u32(bar)) : "memory");
 }
 
+// 2-D tiled store / element-wise add shared memory -> global through the TMA unit
+// (bulk async-group completion).  The tile in shared memory has the layout the
+// tensor map describes (here: 128-byte rows, 128-byte swizzle); x is the innermost
+// coordinate and must be a multiple of 16 bytes / element size.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *smem_src,
+        int32_t x, int32_t y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+            :: "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+            : "memory");
+}
+
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, const void *smem_src,
+        int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+            :: "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+            : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// all committed bulk groups of this thread have finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_all()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void prefetch_l2(const void *p)
 {
     asm volatile("prefetch.global.L2 [%0];" :: "l"(p) : "memory");
