@@ -89,7 +89,7 @@ struct Smem
     float stats[2][2][BLK];              // per Q stage: [0] -lse*log2e, [1] -delta
     uint64_t kv_full;
     uint64_t q_full[2], q_empty[2], g_full[2], g_empty[2];
-    uint64_t s_full, dp_full, p_full, ds_full, dq_full, dq_empty, acc_full;
+    uint64_t s_full, dp_full, p_full, ds_full, dq_full, dq_empty, acc_full, dv_full;
     uint32_t tmem_base;
     uint32_t abort_flag;
     int nact;
@@ -270,7 +270,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         float scale, const bf16 *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
         const float *__restrict__ delta, const float *__restrict__ lse2,
         float *__restrict__ acc_lo, float *__restrict__ acc_hi, Index half_rows,
-        bf16 *__restrict__ dK, bf16 *__restrict__ dV, uint32_t *status)
+        uint32_t *status)
 {
     constexpr bool ALIAS = D == 128;     // dQ_i lives in the dP^T columns
     // At head 128 the MMA produces dQ_i^T (lanes = head elements), so that the 32
@@ -316,6 +316,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         mbar_init(&sm.dq_full, 1);
         mbar_init(&sm.dq_empty, 128);
         mbar_init(&sm.acc_full, 1);
+        mbar_init(&sm.dv_full, 1);
         sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(status) != 0u ? 1u : 0u;
         fence_mbar_init();
         prefetch_tensormap(&tmap_k);
@@ -435,6 +436,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 tc_fence_after_sync();
                 issue_ts<D>(dv_tm, st_tm, sm.g[0], false);           // dV = P^T(0) dO
                 tc_commit(&sm.g_empty[0]);
+                if(nact == 1)
+                {
+                    tc_commit(&sm.dv_full);      // dV is complete one step before dK
+                }
             }
             if(ok && nact > 1)
             {
@@ -528,6 +533,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);       // dV += P^T(n+1) dO
                 }
                 tc_commit(&sm.g_empty[s2]);
+                if(n + 2 == nact)
+                {
+                    tc_commit(&sm.dv_full);
+                }
                 PROF_T(m7);
                 if(n + 2 < nact)
                 {
@@ -835,7 +844,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const int sf = nact & 1;
         if(ok && nact > 0)
         {
-            ok = mbar_wait(&sm.acc_full, 0, abort_flag);
+            // the last dV product is issued a whole step before the last dK, dQ
+            ok = mbar_wait(h == 0 ? &sm.dv_full : &sm.acc_full, 0, abort_flag);
         }
         if(ok && nact >= 2)
         {
@@ -852,24 +862,25 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t src = (h == 0 ? dv_tm : dk_tm) + lane_sel;
             const float mult = h == 0 ? 1.0f : scale;
 #pragma unroll
-            for(int cc = 0; cc < D/32; ++cc)
+            for(int p = 0; p < PANELS; ++p)
             {
-                uint32_t o[32];
-                tmem_ld32(src + 32*cc, o);
+                // one 64-column panel per round: pieces 0..7 of the panel's 128-byte rows
+                uint32_t o[2][32];
+                tmem_ld32(src + 64*p, o[0]);
+                tmem_ld32(src + 64*p + 32, o[1]);
                 tmem_ld_wait();
-                // columns 32cc .. 32cc+31 = pieces 4*(cc & 1) .. +3 of panel cc >> 1
-                uint8_t *prow = stage + (cc >> 1)*4096 + lane*128;
+                uint8_t *prow = stage + p*4096 + lane*128;
 #pragma unroll
-                for(int g4 = 0; g4 < 4; ++g4)
+                for(int g8 = 0; g8 < 8; ++g8)
                 {
                     uint32_t w[4];
 #pragma unroll
                     for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        w[e2] = pack_bf16x2(__uint_as_float(o[8*g4 + 2*e2])*mult,
-                                __uint_as_float(o[8*g4 + 2*e2 + 1])*mult);
+                        w[e2] = pack_bf16x2(__uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2])*mult,
+                                __uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2 + 1])*mult);
                     }
-                    *reinterpret_cast<uint4 *>(prow + (((4*(cc & 1) + g4) ^ (lane & 7)) << 4)) =
+                    *reinterpret_cast<uint4 *>(prow + ((g8 ^ (lane & 7)) << 4)) =
                             make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
@@ -994,7 +1005,7 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
     flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg, tdk, tdv,
             (int)seq, (int)batch, gsz, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
-            acc_lo, acc_hi, half_rows, dK, dV, reinterpret_cast<uint32_t *>(sc));
+            acc_lo, acc_hi, half_rows, reinterpret_cast<uint32_t *>(sc));
     if(launch_status() != NNTILE_B200_OK)
     {
         return NNTILE_B200_E_LAUNCH;

@@ -192,6 +192,7 @@ template<int D>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+        const __grid_constant__ CUtensorMap tmap_a,
         int seq, int batch, int gsz, float scale_log2, const bf16 *__restrict__ mask,
         uint8_t *scratch, float *__restrict__ lse, bf16 *__restrict__ A)
 {
@@ -232,6 +233,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
+        prefetch_tensormap(&tmap_a);
     }
     if(warp == 1)
     {
@@ -464,6 +466,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         int n = 0;
         bool ok = true;
         uint32_t s_phase = 0;
+        // the stored lse of this row is only needed by the epilogue: fetch it now
+        float lse_old = 0.0f;
+        if(nact > 0)
+        {
+            lse_old = lse[(size_t)b*seq + (size_t)qb*BLK + r];
+        }
+        asm volatile("" : "+f"(lse_old));
         for(int it = 0; it < nproc && ok && n < nact; ++it)
         {
             const uint8_t c = sm.cls[t][it];
@@ -630,7 +639,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             float w_dst = 0.0f, w_src = 0.0f;
             if(live)
             {
-                const float old = lse[R];
+                const float old = lse_old;
                 float e, big;
                 if(old > in)
                 {
@@ -649,34 +658,57 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 lse[R] = big + logf(1.0f + e);
             }
             const float inv = live ? 1.0f/l : 0.0f;
-            // TMEM hands a thread one row, global memory wants a warp on consecutive
-            // bytes (one row per lane costs 32 L1 wavefronts per instruction): the
-            // normalised tile result, rounded to storage as the reference's scratch
-            // output is, goes through this warp's 32 rows of the Q tile, which no MMA
-            // reads any more; 16-byte pieces are XOR-swizzled with the row so that the
-            // row-per-lane writes and the row-major reads are both conflict-free.
-            constexpr int PITCH = D*2;
-            uint8_t *stage = sm.q[t] + (warp & 3)*(32*PITCH);
+            // The normalised tile result, rounded to storage as the reference's scratch
+            // output is, goes into this warp's 32 rows of the Q tile (no MMA reads it
+            // any more) as 64-column panels with 128-byte rows in the 128-byte swizzle
+            // of the tensor map.  When every row of the warp simply replaces the stored
+            // one (lse was -inf: first K/V tile of this Q tile), one lane hands the
+            // panels to the TMA unit as a store; otherwise the warp merges row-major
+            // (TMEM gives a thread one row, global memory wants a warp on consecutive
+            // bytes: one row per lane would cost 32 L1 wavefronts per instruction).
+            constexpr int PANELS = D/64;
+            uint8_t *stage = sm.q[t] + (warp & 3)*(PANELS*4096);
 #pragma unroll
-            for(int cc = 0; cc < D/32; ++cc)
+            for(int p = 0; p < PANELS; ++p)
             {
-                uint32_t o[32];
-                tmem_ld32(o_tm + 32*cc, o);
+                uint32_t o[2][32];
+                tmem_ld32(o_tm + 64*p, o[0]);
+                tmem_ld32(o_tm + 64*p + 32, o[1]);
                 tmem_ld_wait();
+                uint8_t *prow = stage + p*4096 + lane*128;
 #pragma unroll
-                for(int g = 0; g < 4; ++g)
+                for(int g8 = 0; g8 < 8; ++g8)
                 {
                     uint32_t w[4];
 #pragma unroll
                     for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        w[e2] = pack_bf16x2(__uint_as_float(o[8*g + 2*e2])*inv,
-                                __uint_as_float(o[8*g + 2*e2 + 1])*inv);
+                        w[e2] = pack_bf16x2(__uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2])*inv,
+                                __uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2 + 1])*inv);
                     }
-                    *reinterpret_cast<uint4 *>(stage + lane*PITCH + (((4*cc + g) ^ (lane & 7)) << 4)) =
+                    *reinterpret_cast<uint4 *>(prow + ((g8 ^ (lane & 7)) << 4)) =
                             make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
+            const bool replace_all = __all_sync(0xffffffffu, live && w_dst == 0.0f);
+            if(replace_all)
+            {
+                fence_proxy_async();
+                __syncwarp();
+                if(lane == 0)
+                {
+                    const int row0 = row_base + qb*BLK + 32*(warp & 3);
+#pragma unroll
+                    for(int p = 0; p < PANELS; ++p)
+                    {
+                        tma_store_2d(&tmap_a, stage + p*4096, 64*p, row0);
+                    }
+                    bulk_commit_group();
+                    bulk_wait_read_all();
+                }
+            }
+            else
+            {
             __syncwarp();
             constexpr int LPR = D/8;                  // lanes (16-byte pieces) per row
             constexpr int RPI = 32/LPR;               // rows per warp instruction
@@ -705,8 +737,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 for(int j = 0; j < 8; ++j)
                 {
                     const int row = base + j*RPI + sub;
-                    const uint4 g = *reinterpret_cast<const uint4 *>(
-                            stage + row*PITCH + ((piece ^ (row & 7)) << 4));
+                    const uint4 g = *reinterpret_cast<const uint4 *>(stage + (piece >> 3)*4096
+                            + row*128 + (((piece & 7) ^ (row & 7)) << 4));
                     const uint32_t pw[4] = {prev[j].x, prev[j].y, prev[j].z, prev[j].w};
                     const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
                     uint32_t outw[4];
@@ -725,6 +757,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                 make_uint4(outw[0], outw[1], outw[2], outw[3]);
                     }
                 }
+            }
             }
         }
         if(!ok && lane == 0)
@@ -776,10 +809,11 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
         const bf16 *mask, const bf16 *V, float *lse, bf16 *A, uint8_t *scratch)
 {
     using namespace fwd;
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, ta;
     const uint64_t rows = (uint64_t)batch*seq;
     if(!make_tmap_bf16_sw128(&tq, Q, rows, D, BLK) || !make_tmap_bf16_sw128(&tk, K, rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK))
+            || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK)
+            || !make_tmap_bf16_sw128(&ta, A, rows, D, 32))
     {
         return NNTILE_B200_E_LAUNCH;
     }
@@ -799,7 +833,7 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     const float scale_log2 = LOG2E_F/sqrtf((float)D);
     // Q, K, V, A of one batch entry
     const int gsz = l2_group_size(batch, (size_t)seq*D*2*4);
-    flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, (int)seq, (int)batch, gsz,
+    flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, ta, (int)seq, (int)batch, gsz,
             scale_log2, mask, scratch, lse, A);
     return launch_status();
 }
