@@ -317,10 +317,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         mbar_init(&sm.dq_empty, 128);
         mbar_init(&sm.acc_full, 1);
         mbar_init(&sm.dv_full, 1);
-        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(status) != 0u ? 1u : 0u;
         fence_mbar_init();
-        prefetch_tensormap(&tmap_k);
-        prefetch_tensormap(&tmap_v);
+        // K and V of this key block are wanted whatever the class table says: their
+        // copies start now, under the set-up of the other warps (a CTA with nothing
+        // to do waits for them in the tear-down)
+        mbar_arrive_expect_tx(&sm.kv_full, 2*Smem<D>::TILE_BYTES);
+        load_tile<D>(sm.k, &tmap_k, &sm.kv_full, row_base + kb*BLK);
+        load_tile<D>(sm.v, &tmap_v, &sm.kv_full, row_base + kb*BLK);
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_g);
         prefetch_tensormap(&tmap_dk);
@@ -330,7 +333,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     {
         tmem_alloc(&sm.tmem_base, 512);
     }
-    if(warp == 0)
+    if(warp == 2 && lane == 0)
+    {
+        // a CTA of this launch that gave up earlier tells the others to skip their work
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(status) != 0u ? 1u : 0u;
+    }
+    if(warp == 3)
     {
         int count = 0;
         for(int base = 0; base < nblk; base += 32)
@@ -373,9 +381,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if(lane == 0 && nact > 0)
         {
             bool ok = true;
-            mbar_arrive_expect_tx(&sm.kv_full, 2*TILE_BYTES);
-            load_tile<D>(sm.k, &tmap_k, &sm.kv_full, row_base + kb*BLK);
-            load_tile<D>(sm.v, &tmap_v, &sm.kv_full, row_base + kb*BLK);
             int n = 0;
             for(int qb = 0; qb < nblk && ok; ++qb)
             {
@@ -916,6 +921,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     // ---- tear-down ---------------------------------------------------------------
     PROF_FLUSH;
+    if(tid == 0)
+    {
+        // the K/V copies issued at the start must have landed before the shared
+        // memory goes away, also when nobody needed them
+        mbar_wait(&sm.kv_full, 0, abort_flag);
+    }
     if(*abort_flag != 0u && tid == 0)
     {
         for(int i = 0; i < 64; ++i)

@@ -227,10 +227,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(&sm.v_full[i], 1);
             mbar_init(&sm.v_empty[i], 1);
         }
-        // a CTA of this launch that gave up earlier tells the others to skip their work
-        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(scratch) != 0u ? 1u : 0u;
         fence_mbar_init();
-        prefetch_tensormap(&tmap_q);
+        // The two Q tiles are wanted whatever the class table says (a tile without
+        // any unmasked block is rare): their copies start now, under the set-up of
+        // the other warps, and the tear-down waits for them in any case.
+        mbar_arrive_expect_tx(&sm.q_full[0], Smem<D>::TILE_BYTES);
+        load_tile<D>(sm.q[0], &tmap_q, &sm.q_full[0], b*seq + qb0*BLK);
+        if(has1)
+        {
+            mbar_arrive_expect_tx(&sm.q_full[1], Smem<D>::TILE_BYTES);
+            load_tile<D>(sm.q[1], &tmap_q, &sm.q_full[1], b*seq + qb1*BLK);
+        }
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
         prefetch_tensormap(&tmap_a);
@@ -239,7 +246,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     {
         tmem_alloc(&sm.tmem_base, 512);
     }
-    if(warp == 0)
+    if(warp == 2 && lane == 0)
+    {
+        // a CTA of this launch that gave up earlier tells the others to skip their work
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(scratch) != 0u ? 1u : 0u;
+    }
+    if(warp == 3)
     {
         // compact the key blocks at least one tile needs (ballot compaction)
         int count = 0, n0 = 0, n1 = 0;
@@ -294,16 +306,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if(lane == 0 && nproc > 0)
         {
             bool ok = true;
-            if(sm.nact[0] > 0)
-            {
-                mbar_arrive_expect_tx(&sm.q_full[0], TILE_BYTES);
-                load_tile<D>(sm.q[0], &tmap_q, &sm.q_full[0], row_base + qb0*BLK);
-            }
-            if(sm.nact[1] > 0)
-            {
-                mbar_arrive_expect_tx(&sm.q_full[1], TILE_BYTES);
-                load_tile<D>(sm.q[1], &tmap_q, &sm.q_full[1], row_base + qb1*BLK);
-            }
             for(int it = 0; it < nproc && ok; ++it)
             {
                 const int st = it % KV_STAGES;
@@ -766,6 +768,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     }
     // ---- tear-down ---------------------------------------------------------------
+    if(tid == 0)
+    {
+        // the Q copies issued at the start must have landed before the shared memory
+        // goes away, also when nobody needed them
+        mbar_wait(&sm.q_full[0], 0, abort_flag);
+        if(has1)
+        {
+            mbar_wait(&sm.q_full[1], 0, abort_flag);
+        }
+    }
     if(*abort_flag != 0u && tid == 0)
     {
         // give copies still in flight time to land before the CTA's memory goes away
