@@ -42,6 +42,9 @@
 // library allocates nothing.  All waits are bounded (sm100.cuh).
 #include "flash.cuh"
 #include "sm100.cuh"
+#ifdef NB200_PROF
+#include <cstdio>
+#endif
 
 namespace nb200 {
 
@@ -52,6 +55,8 @@ namespace bwd {
 // Optional cycle accounting of the roles (build with -DNB200_PROF).
 #ifdef NB200_PROF
 __device__ unsigned long long g_prof[32];
+__device__ unsigned long long g_edge[8];
+__device__ unsigned long long g_edge0[8];
 #define PROF_T(var) const long long var = clock64()
 #define PROF_DECL unsigned long long prof_loc[32]; for(int i_ = 0; i_ < 32; ++i_) prof_loc[i_] = 0
 #define PROF_ADD(slot, a, b) prof_loc[slot] += (unsigned long long)((b) - (a))
@@ -93,7 +98,8 @@ struct Smem
     uint32_t tmem_base;
     uint32_t abort_flag;
     int nact;
-    uint8_t cls[MAX_BLOCKS];             // class of (query block qb, this key block)
+    uint8_t qlist[MAX_BLOCKS];           // query blocks that see this key block, in order
+    uint8_t qcls[MAX_BLOCKS];            // and the class of each (never CLS_SKIP)
 };
 
 // delta[r] = -sum_h A[r,h]*dA[r,h];  lse2[r] = -lse[r]*log2(e)  (both are only ever
@@ -298,6 +304,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     volatile uint32_t *abort_flag = &sm.abort_flag;
     PROF_DECL;
     PROF_T(c0);
+#ifdef NB200_PROF
+    const unsigned long long gt0 = global_timer_ns();
+#endif
 
     if(tid == 0)
     {
@@ -340,6 +349,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     if(warp == 3)
     {
+        // compact list of the query blocks with anything unmasked against this key
+        // block (ballot compaction); the roles below walk the list, not the table
+        static_assert(MAX_BLOCKS <= 256, "query block numbers are stored in bytes");
         int count = 0;
         for(int base = 0; base < nblk; base += 32)
         {
@@ -348,9 +360,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if(qb < nblk)
             {
                 c = cls_tab[(size_t)qb*nblk + kb];
-                sm.cls[qb] = c;
             }
-            count += __popc(__ballot_sync(0xffffffffu, c != CLS_SKIP));
+            const uint32_t m = __ballot_sync(0xffffffffu, c != CLS_SKIP);
+            if(c != CLS_SKIP)
+            {
+                const int pos = count + __popc(m & ((1u << lane) - 1u));
+                sm.qlist[pos] = (uint8_t)qb;
+                sm.qcls[pos] = c;
+            }
+            count += __popc(m);
         }
         if(lane == 0)
         {
@@ -382,16 +400,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         {
             bool ok = true;
             int n = 0;
-            for(int qb = 0; qb < nblk && ok; ++qb)
+            for(int qi = 0; qi < nact && ok; ++qi)
             {
-                if(sm.cls[qb] == CLS_SKIP)
-                {
-                    continue;
-                }
+                const int qb = sm.qlist[qi];
                 const int st = n & 1;
                 const uint32_t ph = (uint32_t)(n >> 1) & 1u;
                 ok = mbar_wait(&sm.q_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
+#ifdef NB200_PROF
+                if(n == 0) atomicAdd(&g_edge0[7], (unsigned long long)(clock64() - c1));
+#endif
                 mbar_arrive_expect_tx(&sm.q_full[st], TILE_BYTES + 2*BLK*4);
                 load_tile<D>(sm.q[st], &tmap_q, &sm.q_full[st], row_base + qb*BLK);
                 bulk_load_1d(sm.stats[st][0], lse2 + (Index)row_base + (Index)qb*BLK, BLK*4,
@@ -586,12 +604,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const uint32_t src = dq_tm + ((uint32_t)(32*(warp & 3)) << 16);
         bool ok = true;
         int n = 0;
-        for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
+        for(int qi = 0; qi < nact && ok; ++qi)
         {
-            if(sm.cls[qb] == CLS_SKIP)
-            {
-                continue;
-            }
+            const int qb = sm.qlist[qi];
             PROF_T(d0);
             ok = mbar_wait(&sm.dq_full, (uint32_t)n & 1u, abort_flag);
             if(!ok) break;
@@ -683,13 +698,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
         bool ok = true;
         int n = 0;
-        for(int qb = 0; qb < nblk && ok && n < nact; ++qb)
+        PROF_T(sentry);
+#ifdef NB200_PROF
+        if(ts == 0) atomicAdd(&g_edge0[6], (unsigned long long)(sentry - c1));
+#endif
+        for(int qi = 0; qi < nact && ok; ++qi)
         {
-            const uint8_t c = sm.cls[qb];
-            if(c == CLS_SKIP)
-            {
-                continue;
-            }
+            const int qb = sm.qlist[qi];
+            const uint8_t c = sm.qcls[qi];
             // -lse*log2e and -delta of the query block arrive with the Q tile (bulk
             // copies on the same barrier); this thread handles 64 of the 128 queries
             PROF_T(sq);
@@ -820,6 +836,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_full);
 #ifdef NB200_PROF
+            if(ts == 0 && !(n >= 2 && n + 2 < nact))
+            {
+                PROF_T(s4x);
+                // iterations outside the steady state, by position (first wins)
+                const int slot = n == 0 ? 0 : n == 1 ? 1 : n + 1 == nact ? 3 : 2;
+                atomicAdd(&g_edge[slot], (unsigned long long)(s4x - sq));
+                atomicAdd(&g_edge[4 + slot], 1ull);
+                if(n == 0)
+                {
+                    atomicAdd(&g_edge0[0], (unsigned long long)(sq - c1));   // sync -> loop top
+                    atomicAdd(&g_edge0[1], (unsigned long long)(s0 - sq));   // wait Q
+                    atomicAdd(&g_edge0[2], (unsigned long long)(s1 - s0));   // wait S
+                    atomicAdd(&g_edge0[3], (unsigned long long)(s2 - s1));   // A
+                    atomicAdd(&g_edge0[4], (unsigned long long)(s3 - s2));   // wait dP
+                    atomicAdd(&g_edge0[5], (unsigned long long)(s4x - s3));  // B
+                }
+            }
             if(ts == 0 && n >= 2 && n + 2 < nact)
             {
                 PROF_T(s4);
@@ -940,6 +973,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     {
         tmem_dealloc(tmem, 512);
     }
+#ifdef NB200_PROF
+    if(tid == 0)
+    {
+        const unsigned long long gt1 = global_timer_ns();
+        atomicAdd(&g_prof[26], gt1 - gt0);          // sum of CTA lifetimes (ns)
+        atomicMin(&g_prof[27], gt0);                // first CTA start
+        atomicMax(&g_prof[28], gt1);                // last CTA end
+    }
+#endif
 }
 
 } // namespace bwd
@@ -949,9 +991,26 @@ extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out32, int reset)
 {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out32, bwd::g_prof, sizeof(unsigned long long)*32);
+    {
+        unsigned long long e[8];
+        cudaMemcpyFromSymbol(e, bwd::g_edge, sizeof(e));
+        printf("  edge iterations (clk): n=0 %.0f  n=1 %.0f  middle-edge %.0f  last %.0f\n",
+                e[4] ? (double)e[0]/e[4] : 0.0, e[5] ? (double)e[1]/e[5] : 0.0,
+                e[6] ? (double)e[2]/e[6] : 0.0, e[7] ? (double)e[3]/e[7] : 0.0);
+        unsigned long long z8[8] = {0};
+        cudaMemcpyToSymbol(bwd::g_edge, z8, sizeof(z8));
+        unsigned long long f[8];
+        cudaMemcpyFromSymbol(f, bwd::g_edge0, sizeof(f));
+        const double n0 = e[4] ? (double)e[4] : 1.0;
+        printf("  sync->softmax entry %.0f, sync->first Q copy issued %.0f\n", f[6]/n0, f[7]/n0);
+        printf("  n=0: sync->top %.0f waitQ %.0f waitS %.0f A %.0f wait_dP %.0f B %.0f\n",
+                f[0]/n0, f[1]/n0, f[2]/n0, f[3]/n0, f[4]/n0, f[5]/n0);
+        cudaMemcpyToSymbol(bwd::g_edge0, z8, sizeof(z8));
+    }
     if(reset)
     {
         unsigned long long z[32] = {0};
+        z[27] = ~0ull;
         cudaMemcpyToSymbol(bwd::g_prof, z, sizeof(z));
     }
 }
@@ -1004,6 +1063,7 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     {
         return NNTILE_B200_E_LAUNCH;
     }
+    static_assert(sizeof(Smem<D>) <= 232448, "Smem exceeds the 227 KB a CTA can have");
     static const size_t smem_bytes = sizeof(Smem<D>);
     static const cudaError_t attr = cudaFuncSetAttribute(flash_bwd_kernel<D>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
