@@ -42,9 +42,6 @@
 // library allocates nothing.  All waits are bounded (sm100.cuh).
 #include "flash.cuh"
 #include "sm100.cuh"
-#ifdef NB200_PROF
-#include <cstdio>
-#endif
 
 namespace nb200 {
 
@@ -55,8 +52,6 @@ namespace bwd {
 // Optional cycle accounting of the roles (build with -DNB200_PROF).
 #ifdef NB200_PROF
 __device__ unsigned long long g_prof[32];
-__device__ unsigned long long g_edge[8];
-__device__ unsigned long long g_edge0[8];
 #define PROF_T(var) const long long var = clock64()
 #define PROF_DECL unsigned long long prof_loc[32]; for(int i_ = 0; i_ < 32; ++i_) prof_loc[i_] = 0
 #define PROF_ADD(slot, a, b) prof_loc[slot] += (unsigned long long)((b) - (a))
@@ -407,9 +402,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 const uint32_t ph = (uint32_t)(n >> 1) & 1u;
                 ok = mbar_wait(&sm.q_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
-#ifdef NB200_PROF
-                if(n == 0) atomicAdd(&g_edge0[7], (unsigned long long)(clock64() - c1));
-#endif
                 mbar_arrive_expect_tx(&sm.q_full[st], TILE_BYTES + 2*BLK*4);
                 load_tile<D>(sm.q[st], &tmap_q, &sm.q_full[st], row_base + qb*BLK);
                 bulk_load_1d(sm.stats[st][0], lse2 + (Index)row_base + (Index)qb*BLK, BLK*4,
@@ -698,10 +690,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const uint32_t lane_sel = (uint32_t)(32*(warp & 3)) << 16;
         bool ok = true;
         int n = 0;
-        PROF_T(sentry);
-#ifdef NB200_PROF
-        if(ts == 0) atomicAdd(&g_edge0[6], (unsigned long long)(sentry - c1));
-#endif
         for(int qi = 0; qi < nact && ok; ++qi)
         {
             const int qb = sm.qlist[qi];
@@ -836,23 +824,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_full);
 #ifdef NB200_PROF
-            if(ts == 0 && !(n >= 2 && n + 2 < nact))
-            {
-                PROF_T(s4x);
-                // iterations outside the steady state, by position (first wins)
-                const int slot = n == 0 ? 0 : n == 1 ? 1 : n + 1 == nact ? 3 : 2;
-                atomicAdd(&g_edge[slot], (unsigned long long)(s4x - sq));
-                atomicAdd(&g_edge[4 + slot], 1ull);
-                if(n == 0)
-                {
-                    atomicAdd(&g_edge0[0], (unsigned long long)(sq - c1));   // sync -> loop top
-                    atomicAdd(&g_edge0[1], (unsigned long long)(s0 - sq));   // wait Q
-                    atomicAdd(&g_edge0[2], (unsigned long long)(s1 - s0));   // wait S
-                    atomicAdd(&g_edge0[3], (unsigned long long)(s2 - s1));   // A
-                    atomicAdd(&g_edge0[4], (unsigned long long)(s3 - s2));   // wait dP
-                    atomicAdd(&g_edge0[5], (unsigned long long)(s4x - s3));  // B
-                }
-            }
             if(ts == 0 && n >= 2 && n + 2 < nact)
             {
                 PROF_T(s4);
@@ -991,22 +962,6 @@ extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out32, int reset)
 {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out32, bwd::g_prof, sizeof(unsigned long long)*32);
-    {
-        unsigned long long e[8];
-        cudaMemcpyFromSymbol(e, bwd::g_edge, sizeof(e));
-        printf("  edge iterations (clk): n=0 %.0f  n=1 %.0f  middle-edge %.0f  last %.0f\n",
-                e[4] ? (double)e[0]/e[4] : 0.0, e[5] ? (double)e[1]/e[5] : 0.0,
-                e[6] ? (double)e[2]/e[6] : 0.0, e[7] ? (double)e[3]/e[7] : 0.0);
-        unsigned long long z8[8] = {0};
-        cudaMemcpyToSymbol(bwd::g_edge, z8, sizeof(z8));
-        unsigned long long f[8];
-        cudaMemcpyFromSymbol(f, bwd::g_edge0, sizeof(f));
-        const double n0 = e[4] ? (double)e[4] : 1.0;
-        printf("  sync->softmax entry %.0f, sync->first Q copy issued %.0f\n", f[6]/n0, f[7]/n0);
-        printf("  n=0: sync->top %.0f waitQ %.0f waitS %.0f A %.0f wait_dP %.0f B %.0f\n",
-                f[0]/n0, f[1]/n0, f[2]/n0, f[3]/n0, f[4]/n0, f[5]/n0);
-        cudaMemcpyToSymbol(bwd::g_edge0, z8, sizeof(z8));
-    }
     if(reset)
     {
         unsigned long long z[32] = {0};
