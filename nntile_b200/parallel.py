@@ -55,3 +55,54 @@ def max_over_ranks(value: float, device, group=None) -> float:
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
+
+
+def chunk_ranges(n_units: int, chunks: int) -> list[tuple[int, int]]:
+    """[lo, hi) blocks of the leading (kv head) index for `chunks` pipeline stages."""
+    chunks = max(1, min(int(chunks), int(n_units)))
+    return [shard_range(n_units, c, chunks) for c in range(chunks)]
+
+
+class HostStream:
+    """Runs a per-unit body on tensors that live in pinned host memory, with the
+    copies overlapped with the kernels.
+
+    The reference leaves this to StarPU: its codelets are STARPU_CUDA_ASYNC
+    (src/starpu/codelet.cc:80), so the runtime moves the next task's handles to the
+    GPU and the previous task's results back while a task computes.  Here the
+    leading (kv head) index of the buffers is cut into chunks - every kv head is an
+    independent problem - and three streams are chained by events: host-to-device
+    copy of chunk c+1, kernels of chunk c, device-to-host copy of chunk c-1.  PCIe
+    is full duplex, so a step costs about max(copy in, copy out) instead of
+    copy in + kernels + copy out.
+
+    `body(lo, hi)` enqueues the kernels for units [lo, hi) on the current stream;
+    all tensors are indexed by unit along axis 0."""
+
+    def __init__(self, device, n_units: int, chunks: int = 8):
+        self.device = device
+        self.ranges = chunk_ranges(n_units, chunks)
+        self.s_in = torch.cuda.Stream(device=device)
+        self.s_out = torch.cuda.Stream(device=device)
+        self.ev_in = [torch.cuda.Event() for _ in self.ranges]
+        self.ev_done = [torch.cuda.Event() for _ in self.ranges]
+
+    def step(self, host_in, dev_in, body, dev_out, host_out):
+        cur = torch.cuda.current_stream(self.device)
+        # the previous step's kernels must be done with the device buffers
+        self.s_in.wait_stream(cur)
+        for c, (lo, hi) in enumerate(self.ranges):
+            with torch.cuda.stream(self.s_in):
+                for h, d in zip(host_in, dev_in):
+                    d[lo:hi].copy_(h[lo:hi], non_blocking=True)
+                self.ev_in[c].record(self.s_in)
+        for c, (lo, hi) in enumerate(self.ranges):
+            cur.wait_event(self.ev_in[c])
+            body(lo, hi)
+            self.ev_done[c].record(cur)
+            self.s_out.wait_event(self.ev_done[c])
+            with torch.cuda.stream(self.s_out):
+                for h, d in zip(host_out, dev_out):
+                    h[lo:hi].copy_(d[lo:hi], non_blocking=True)
+        # the step is over when its last result is on the host
+        cur.wait_stream(self.s_out)

@@ -62,3 +62,13 @@ def test_shard_units_falls_back_to_batch_axis():
     assert parallel.shard_units(x, 1, 2).shape == (3, 1, 2, 2, 2)
     with pytest.raises(ValueError):
         parallel.shard_units(torch.zeros(3, 1, 3, 2, 2), 0, 2)
+
+
+def test_chunk_ranges_cover_units():
+    from nntile_b200.parallel import chunk_ranges
+    for n, c in ((8, 8), (8, 3), (5, 8), (1, 4), (12, 5)):
+        r = chunk_ranges(n, c)
+        assert len(r) == min(n, c)
+        assert r[0][0] == 0 and r[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(hi > lo for lo, hi in r)
