@@ -188,6 +188,19 @@ int nntile_b200_decode_sdpa_bf16(nntile_b200_stream_t stream, int64_t head,
 size_t nntile_b200_decode_sdpa_workspace_bytes(int64_t head, int64_t length,
         int64_t batch, int64_t group, int64_t kv_heads);
 
+/* Append `new_seq` positions to a KV cache in place:
+ * cache[:, cache_len : cache_len + new_seq, :, :] = src, with src bf16
+ * [head, new_seq, batch, kv_heads] and cache bf16 [head, max_seq, batch, kv_heads].
+ * Replaces the copy_intersection_async call of KVCache.append
+ * (wrappers/python/nntile/layer/cache_utils.py:146-176; kernel
+ * src/kernel/subcopy); together with nntile_b200_decode_sdpa_bf16 reading only the
+ * first `length` positions it also makes KVCache.k_partial / v_partial
+ * (cache_utils.py:178-214: a copy of the filled part per decode step) unnecessary.
+ * Rejected with NNTILE_B200_E_BADARG when cache_len + new_seq > max_seq. */
+int nntile_b200_kv_cache_append_bf16(nntile_b200_stream_t stream, int64_t head,
+        int64_t max_seq, int64_t batch, int64_t kv_heads, int64_t cache_len,
+        int64_t new_seq, const void *src, void *cache);
+
 /* The same operation for callers that cannot hand over a workspace because they
  * cannot allocate device memory where they run: the body of a StarPU codelet or
  * of any other task-runtime worker callback (cudaMalloc there would serialise the

@@ -37,6 +37,7 @@ SIGNATURES = {
     "nntile_b200_flash_sdpa_bwd_path": ([i64, i64, i64], ctypes.c_int),
     "nntile_b200_decode_sdpa_bf16": ([vp] + [i64]*6 + [vp]*6 + [sz], ctypes.c_int),
     "nntile_b200_decode_sdpa_workspace_bytes": ([i64]*5, sz),
+    "nntile_b200_kv_cache_append_bf16": ([vp] + [i64]*6 + [vp]*2, ctypes.c_int),
     "nntile_b200_decode_sdpa_noalloc_bf16": ([vp] + [i64]*6 + [vp]*5, ctypes.c_int),
     "nntile_b200_decode_sdpa_noalloc_max_bytes": ([], sz),
     "nntile_b200_tensor_flash_sdpa_fwd_bf16": ([vp, _pi, _pi] + [_pp]*6 + [vp, sz], ctypes.c_int),

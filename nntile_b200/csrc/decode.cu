@@ -587,3 +587,70 @@ extern "C" int nntile_b200_decode_sdpa_noalloc_bf16(nntile_b200_stream_t stream,
     return nntile_b200_decode_sdpa_bf16(stream, head, max_seq, length, batch, group,
             kv_heads, q, Kcache, Vcache, out, lse_out, scratch, DECODE_SCRATCH_BYTES);
 }
+
+// ------------------------------------------------------------------ cache append
+// cache[:, cache_len : cache_len + new_seq, b, kh] = src[:, :, b, kh] for every
+// (batch entry, kv head): per unit one contiguous run of head*new_seq elements.
+namespace nb200 {
+
+__global__ void __launch_bounds__(256)
+kv_append_kernel(bool vec16, Index run_bytes, Index src_unit_bytes, Index dst_unit_bytes,
+        Index dst_off_bytes, const uint8_t *__restrict__ src, uint8_t *__restrict__ dst)
+{
+    const uint8_t *s = src + (Index)blockIdx.y*src_unit_bytes;
+    uint8_t *d = dst + (Index)blockIdx.y*dst_unit_bytes + dst_off_bytes;
+    const Index stride = (Index)gridDim.x*blockDim.x;
+    const Index first = (Index)blockIdx.x*blockDim.x + threadIdx.x;
+    if(vec16)
+    {
+        for(Index i = first; i < run_bytes/16; i += stride)
+        {
+            reinterpret_cast<uint4 *>(d)[i] = reinterpret_cast<const uint4 *>(s)[i];
+        }
+    }
+    else
+    {
+        for(Index i = first; i < run_bytes/2; i += stride)
+        {
+            reinterpret_cast<uint16_t *>(d)[i] = reinterpret_cast<const uint16_t *>(s)[i];
+        }
+    }
+}
+
+} // namespace nb200
+
+extern "C" int nntile_b200_kv_cache_append_bf16(nntile_b200_stream_t stream, int64_t head,
+        int64_t max_seq, int64_t batch, int64_t kv_heads, int64_t cache_len, int64_t new_seq,
+        const void *src, void *cache)
+{
+    using namespace nb200;
+    if(head < 1 || max_seq < 1 || batch < 1 || kv_heads < 1 || cache_len < 0 || new_seq < 0
+            || cache_len + new_seq > max_seq)
+    {
+        return NNTILE_B200_E_BADARG;        // the append would run past the cache
+    }
+    if(batch*kv_heads > 65535)
+    {
+        return NNTILE_B200_E_SHAPE;
+    }
+    if(new_seq == 0)
+    {
+        return NNTILE_B200_OK;
+    }
+    if(!src || !cache)
+    {
+        return NNTILE_B200_E_BADARG;
+    }
+    if((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(cache)) & 1)
+    {
+        return NNTILE_B200_E_ALIGN;
+    }
+    const Index run = head*new_seq*2, unit = head*max_seq*2, off = head*cache_len*2;
+    const bool vec16 = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(cache)
+            | (uintptr_t)run | (uintptr_t)unit | (uintptr_t)off) & 15) == 0;
+    const unsigned bx = (unsigned)std::min<Index>(64, std::max<Index>(1, run/16/256));
+    kv_append_kernel<<<dim3(bx, (unsigned)(batch*kv_heads)), 256, 0,
+            static_cast<cudaStream_t>(stream)>>>(vec16, run, run, unit, off,
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(cache));
+    return launch_status();
+}

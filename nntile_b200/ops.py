@@ -138,6 +138,11 @@ def flash_sdpa_path(seq, head, batch, backward=False) -> int:
     return int(fn(seq, head, batch))
 
 
+def kv_cache_append(head, max_seq, batch, kv_heads, cache_len, new_seq, src, cache):
+    _call("nntile_b200_kv_cache_append_bf16", _stream(), head, max_seq, batch, kv_heads,
+          cache_len, new_seq, _ptr(src), _ptr(cache))
+
+
 def decode_workspace_bytes(head, length, batch, group, kv_heads) -> int:
     return int(_lib.load().nntile_b200_decode_sdpa_workspace_bytes(head, length, batch, group,
                                                                    kv_heads))

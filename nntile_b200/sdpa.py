@@ -218,3 +218,57 @@ def decode_sdpa(q, Kcache, Vcache, length=None, out=None, lse_out=None, workspac
         workspace = torch.empty(max(n, 16), dtype=torch.uint8, device=q.device)
     ops.decode_sdpa(D, L, length, B, G, H, q, Kcache, Vcache, out, lse_out, workspace)
     return out
+
+
+class KVCache:
+    """Preallocated key/value cache of one attention layer, filled in place.
+
+    Mirrors nntile.layer.cache_utils.KVCache (wrappers/python/nntile/layer/
+    cache_utils.py:118-228): ``append(k_partial, v_partial)``, ``len()``,
+    ``clear()``, attributes ``k`` and ``v``.  Differences, all on purpose: the
+    buffers hold the kv heads only (the reference stores what the attention layer
+    has already replicated ``group`` times), ``append`` writes into the buffer at
+    the current length (one kernel, no re-allocation), and there is no
+    ``k_partial`` / ``v_partial`` copy of the filled part per step: ``decode``
+    hands the whole buffer and the current length to the split-KV kernel.
+
+    Torch shapes: k, v (kv_heads, batch, max_seq, head) = Fortran
+    [head, max_seq, batch, kv_heads]; k_partial, v_partial (kv_heads, batch, new_seq,
+    head); q (kv_heads, group, batch, 1, head)."""
+
+    def __init__(self, max_cache_size: int, kv_heads: int, batch: int, head: int,
+                 device="cuda"):
+        self.max_cache_size = int(max_cache_size)
+        self.k = torch.zeros((kv_heads, batch, self.max_cache_size, head), dtype=torch.bfloat16,
+                             device=device)
+        self.v = torch.zeros_like(self.k)
+        self.k_cache_size = 0
+        self.v_cache_size = 0
+        self._workspace = None
+
+    def append(self, k_partial: torch.Tensor, v_partial: torch.Tensor):
+        H, B, L, D = self.k.shape
+        if k_partial.shape != v_partial.shape or k_partial.shape[:2] != (H, B) \
+                or k_partial.shape[3] != D:
+            raise ValueError("k_partial / v_partial do not match the cache")
+        n = k_partial.shape[2]
+        ops.kv_cache_append(D, L, B, H, self.k_cache_size, n, k_partial.contiguous(), self.k)
+        ops.kv_cache_append(D, L, B, H, self.v_cache_size, n, v_partial.contiguous(), self.v)
+        self.k_cache_size += n
+        self.v_cache_size += n
+
+    def decode(self, q: torch.Tensor, out=None, lse_out=None):
+        """Attention of one new query token per (batch, head) over the filled part."""
+        H, G, B, one, D = q.shape
+        need = ops.decode_workspace_bytes(D, max(self.k_cache_size, 1), B, G, H)
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+        return decode_sdpa(q, self.k, self.v, length=self.k_cache_size, out=out,
+                           lse_out=lse_out, workspace=self._workspace)
+
+    def clear(self):
+        self.k_cache_size = 0
+        self.v_cache_size = 0
+
+    def __len__(self):
+        return self.k_cache_size

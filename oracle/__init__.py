@@ -455,3 +455,15 @@ def rel_err(actual, reference) -> float:
     r = np.asarray(reference, dtype=np.float64)
     den = np.linalg.norm(r)
     return float(np.linalg.norm(a - r) / (den if den != 0 else 1.0))
+
+
+def kv_cache_append(cache, cache_len, partial):
+    """wrappers/python/nntile/layer/cache_utils.py:146-176: KVCache.append copies
+    k_partial / v_partial [D, n, B, H] into the preallocated cache [D, L, B, H] at
+    sequence offset `cache_len` (copy_intersection_async).  In place; returns the
+    new length."""
+    n = partial.shape[1]
+    if cache_len + n > cache.shape[1]:
+        raise ValueError("append past the end of the cache")
+    cache[:, cache_len:cache_len + n] = partial
+    return cache_len + n

@@ -76,3 +76,52 @@ def test_decode_rejects_small_workspace():
     with pytest.raises(_lib.StatusError) as e:
         decode_sdpa(q, Kc, Kc, workspace=ws)
     assert e.value.status == -4
+
+
+def test_kv_cache_prefill_append_decode_loop():
+    """KVCache: prefill append, then token-by-token append + decode, against the
+    reference's cache semantics (append = copy at the current length) and its
+    decode chain on the filled part.  Bit-exact for the cache contents."""
+    from nntile_b200.sdpa import KVCache
+    D, L, B, G, H = 128, 640, 2, 4, 2
+    rng = np.random.default_rng(11)
+    dev = torch.device("cuda", 0)
+    cache = KVCache(L, H, B, D, device=dev)
+    Kref = O.to_bf16(np.zeros((D, L, B, H), dtype=np.float32, order="F"))
+    Vref = Kref.copy(order="F")
+    n_ref = 0
+
+    def new_kv(n):
+        k = O.to_bf16(np.asfortranarray(rng.standard_normal((D, n, B, H)).astype(np.float32)))
+        v = O.to_bf16(np.asfortranarray(rng.standard_normal((D, n, B, H)).astype(np.float32)))
+        return k, v
+
+    for n in (300, 1, 1, 7, 1):                  # prefill, then decode steps
+        k, v = new_kv(n)
+        cache.append(from_fortran(k, dev), from_fortran(v, dev))
+        O.kv_cache_append(Kref, n_ref, k)
+        n_ref = O.kv_cache_append(Vref, n_ref, v)
+        assert len(cache) == n_ref
+        assert np.array_equal(to_fortran(cache.k).view(np.uint16), Kref.view(np.uint16))
+        assert np.array_equal(to_fortran(cache.v).view(np.uint16), Vref.view(np.uint16))
+        q = O.to_bf16(np.asfortranarray(
+            rng.standard_normal((D, 1, B, G, H)).astype(np.float32)))
+        got = O.from_bf16(to_fortran(cache.decode(from_fortran(q, dev))))
+        want = O.from_bf16(O.decode_chain(q, Kref, Vref, length=n_ref))
+        assert O.rel_err(got, want) <= 2e-2      # bf16 storage, fp32 accumulation
+    cache.clear()
+    assert len(cache) == 0
+
+
+def test_kv_cache_append_rejects_overflow_and_odd_shapes():
+    from nntile_b200 import _lib
+    D, L, B, H = 24, 10, 3, 2                    # rows of 48 bytes: element-wise path
+    dev = torch.device("cuda", 0)
+    cache = torch.zeros((H, B, L, D), dtype=torch.bfloat16, device=dev)
+    src = torch.randn((H, B, 4, D), device=dev).to(torch.bfloat16)
+    ops.kv_cache_append(D, L, B, H, 3, 4, src, cache)
+    torch.cuda.synchronize()
+    assert torch.equal(cache[:, :, 3:7], src)
+    assert float(cache[:, :, :3].abs().sum()) == 0.0 and float(cache[:, :, 7:].abs().sum()) == 0.0
+    with pytest.raises(_lib.StatusError):
+        ops.kv_cache_append(D, L, B, H, 8, 4, src, cache)

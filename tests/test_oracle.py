@@ -198,3 +198,21 @@ def test_decode_chain_against_fp64():
     Vr = np.repeat(O.from_bf16(Vc)[:, :150, :, None, :], G, axis=3)
     a64, _ = O.sdpa_fp64(O.from_bf16(q), Kr, Vr, np.zeros((150, 1), np.float32))
     assert O.rel_err(O.from_bf16(Y), a64) <= 2e-2
+
+
+def test_kv_cache_append_restatement():
+    """KVCache.append semantics (cache_utils.py:146-176): copy at the current
+    length, lengths add up, appending past max_cache_size is an error."""
+    import oracle as O
+    rng = np.random.default_rng(3)
+    cache = np.zeros((8, 10, 2, 3), dtype=np.float32, order="F")
+    n = 0
+    parts = []
+    for m in (4, 1, 5):
+        p = np.asfortranarray(rng.standard_normal((8, m, 2, 3)).astype(np.float32))
+        n = O.kv_cache_append(cache, n, p)
+        parts.append(p)
+    assert n == 10
+    assert np.array_equal(cache, np.concatenate(parts, axis=1))
+    with pytest.raises(ValueError):
+        O.kv_cache_append(cache, n, parts[1])
