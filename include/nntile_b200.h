@@ -161,7 +161,31 @@ int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int64_t seq,
         void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ,
         void *dV);
 
-/* Which implementation the two entry points above pick for a shape:
+/* Grouped-query form of the two tile tasks above: Q, A, dA, dQ are
+ * [head, seq, batch, group, kv_heads], K, V, dK, dV are [head, seq, batch, kv_heads]
+ * and are NOT replicated over the group.  The reference has no such entry point: its
+ * attention layers replicate K and V `group` times before the SDPA layer and sum the
+ * K/V gradients over the group afterwards (wrappers/python/nntile/model/
+ * llama_attention.py:605-616, 786-793: add_slice_inplace forward, sum_slice
+ * backward); calling these instead drops both passes and reads K/V once per kv
+ * head.  Same mask, lse and merge / "+=" contracts as the entry points above; dK and
+ * dV receive the sum over the group.  Only shapes the tcgen05 kernels take (head 64
+ * or 128, seq a multiple of 128), NNTILE_B200_E_SHAPE otherwise.  `scratch` holds at
+ * least nntile_b200_flash_sdpa_gqa_scratch_bytes(...) bytes for the backward and
+ * 256 + (seq/128)^2 bytes for the forward, 16-byte aligned. */
+int nntile_b200_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
+        const void *Q, const void *mask, const void *V, float *lse, void *A,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
+        const void *Q, const void *V, const void *A, const void *dA, const void *mask,
+        const float *lse, void *dK, void *dQ, void *dV, void *scratch,
+        size_t scratch_bytes);
+size_t nntile_b200_flash_sdpa_gqa_scratch_bytes(int64_t seq, int64_t head,
+        int64_t batch, int64_t group, int64_t kv_heads);
+
+/* Which implementation nntile_b200_flash_sdpa_{fwd,bwd}_bf16 pick for a shape:
  * 2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel, 0 = rejected. */
 int nntile_b200_flash_sdpa_fwd_path(int64_t seq, int64_t head, int64_t batch);
 int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_t batch);

@@ -35,6 +35,9 @@ SIGNATURES = {
     "nntile_b200_flash_sdpa_bwd_bf16": ([vp, i64, i64, i64] + [vp]*13, ctypes.c_int),
     "nntile_b200_flash_sdpa_fwd_path": ([i64, i64, i64], ctypes.c_int),
     "nntile_b200_flash_sdpa_bwd_path": ([i64, i64, i64], ctypes.c_int),
+    "nntile_b200_flash_sdpa_fwd_gqa_bf16": ([vp] + [i64]*5 + [vp]*7 + [sz], ctypes.c_int),
+    "nntile_b200_flash_sdpa_bwd_gqa_bf16": ([vp] + [i64]*5 + [vp]*11 + [sz], ctypes.c_int),
+    "nntile_b200_flash_sdpa_gqa_scratch_bytes": ([i64]*5, sz),
     "nntile_b200_decode_sdpa_bf16": ([vp] + [i64]*6 + [vp]*6 + [sz], ctypes.c_int),
     "nntile_b200_decode_sdpa_workspace_bytes": ([i64]*5, sz),
     "nntile_b200_kv_cache_append_bf16": ([vp] + [i64]*6 + [vp]*2, ctypes.c_int),

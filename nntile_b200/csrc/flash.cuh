@@ -17,14 +17,17 @@ int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const bf16 *A, const
 // tcgen05 / TMEM / TMA kernels (flash_fwd_sm100.cu, flash_bwd_sm100.cu):
 // head in {64, 128}, seq a multiple of 128.
 bool flash_fwd_sm100_supports(Index seq, Index head, Index batch);
+// K, V (and dK, dV) may be shared by `kv_group` consecutive groups of `kv_batch`
+// batch entries: entry b uses K/V entry (b % kv_batch) + kv_batch*(b/(kv_batch*kv_group)).
+// kv_group = 1, kv_batch = batch is the plain one-to-one case.
 int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A,
-        void *scratch, size_t scratch_bytes);
+        void *scratch, size_t scratch_bytes, Index kv_group, Index kv_batch);
 bool flash_bwd_sm100_supports(Index seq, Index head, Index batch);
 int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
         const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV,
-        bf16 *dK, bf16 *dQ, bf16 *dV);
+        bf16 *dK, bf16 *dQ, bf16 *dV, Index kv_group, Index kv_batch);
 
 // Classes of a 128x128 block of the additive mask [seq_q][seq_k].
 enum : uint8_t

@@ -43,7 +43,7 @@ extern "C" int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int6
         }
         return flash_fwd_sm100(as_stream(stream), seq, head, batch, (const bf16 *)K,
                 (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A,
-                scratch_A, (size_t)seq*head*batch*sizeof(bf16));
+                scratch_A, (size_t)seq*head*batch*sizeof(bf16), 1, batch);
     }
     return flash_fwd_generic(as_stream(stream), seq, head, batch, (const bf16 *)K,
             (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A);
@@ -79,10 +79,81 @@ extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int6
         return flash_bwd_sm100(as_stream(stream), seq, head, batch, (const bf16 *)K,
                 (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
                 (const bf16 *)mask, lse, scratch_dK, scratch_dQ, scratch_dV,
-                (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV);
+                (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV, 1, batch);
     }
     return flash_bwd_generic(as_stream(stream), seq, head, batch, (const bf16 *)K,
             (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
             (const bf16 *)mask, lse, (float *)scratch_dV, (bf16 *)dK, (bf16 *)dQ,
             (bf16 *)dV);
+}
+
+// ------------------------------------------------------------ grouped-query form
+// Q, A, dA, dQ: [head, seq, batch, group, kv_heads]; K, V, dK, dV: [head, seq, batch,
+// kv_heads] (not replicated over the group).  tcgen05 kernels only.
+static int check_gqa(int64_t seq, int64_t head, int64_t batch, int64_t group, int64_t kv_heads)
+{
+    if(seq < 0 || head < 0 || batch < 0 || group < 0 || kv_heads < 0) return NNTILE_B200_E_BADARG;
+    return NNTILE_B200_OK;
+}
+
+extern "C" size_t nntile_b200_flash_sdpa_gqa_scratch_bytes(int64_t seq, int64_t head,
+        int64_t batch, int64_t group, int64_t kv_heads)
+{
+    if(check_gqa(seq, head, batch, group, kv_heads) != NNTILE_B200_OK) return 0;
+    // status word + class table + delta + lse*log2e in a region the size of one
+    // bf16 tensor, then the fp32 dQ accumulator
+    return (size_t)seq*head*batch*group*kv_heads*6;
+}
+
+extern "C" int nntile_b200_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
+        const void *Q, const void *mask, const void *V, float *lse, void *A, void *scratch,
+        size_t scratch_bytes)
+{
+    int st = check_gqa(seq, head, batch, group, kv_heads);
+    if(st != NNTILE_B200_OK) return st;
+    const int64_t slices = batch*group*kv_heads;
+    if(seq == 0 || head == 0 || slices == 0) return NNTILE_B200_OK;
+    if(!K || !Q || !mask || !V || !lse || !A || !scratch) return NNTILE_B200_E_BADARG;
+    if(!flash_fwd_sm100_supports(seq, head, slices)) return NNTILE_B200_E_SHAPE;
+    if(!aligned16(K) || !aligned16(Q) || !aligned16(V) || !aligned16(A) || !aligned16(mask)
+            || !aligned16(scratch))
+    {
+        return NNTILE_B200_E_ALIGN;
+    }
+    return flash_fwd_sm100(as_stream(stream), seq, head, slices, (const bf16 *)K,
+            (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A, scratch,
+            scratch_bytes, group, batch);
+}
+
+extern "C" int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
+        const void *Q, const void *V, const void *A, const void *dA, const void *mask,
+        const float *lse, void *dK, void *dQ, void *dV, void *scratch, size_t scratch_bytes)
+{
+    int st = check_gqa(seq, head, batch, group, kv_heads);
+    if(st != NNTILE_B200_OK) return st;
+    const int64_t slices = batch*group*kv_heads;
+    if(seq == 0 || head == 0 || slices == 0) return NNTILE_B200_OK;
+    if(!K || !Q || !V || !A || !dA || !mask || !lse || !dK || !dQ || !dV || !scratch)
+    {
+        return NNTILE_B200_E_BADARG;
+    }
+    if(!flash_bwd_sm100_supports(seq, head, slices)) return NNTILE_B200_E_SHAPE;
+    if(scratch_bytes < nntile_b200_flash_sdpa_gqa_scratch_bytes(seq, head, batch, group, kv_heads))
+    {
+        return NNTILE_B200_E_SCRATCH;
+    }
+    if(!aligned16(K) || !aligned16(Q) || !aligned16(V) || !aligned16(A) || !aligned16(dA)
+            || !aligned16(mask) || !aligned16(dK) || !aligned16(dQ) || !aligned16(dV)
+            || !aligned16(scratch))
+    {
+        return NNTILE_B200_E_ALIGN;
+    }
+    const size_t part = (size_t)seq*head*slices*2;        // one bf16 tensor of Q's shape
+    uint8_t *sc = static_cast<uint8_t *>(scratch);
+    return flash_bwd_sm100(as_stream(stream), seq, head, slices, (const bf16 *)K,
+            (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
+            (const bf16 *)mask, lse, sc + 2*part, sc + part, sc, (bf16 *)dK, (bf16 *)dQ,
+            (bf16 *)dV, group, batch);
 }

@@ -267,7 +267,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
         const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_dk,
-        const __grid_constant__ CUtensorMap tmap_dv, int seq, int batch, int gsz, float scale_log2,
+        const __grid_constant__ CUtensorMap tmap_dv, int seq, int batch, int gsz, int kv_group,
+        int kv_batch, float scale_log2,
         float scale, const bf16 *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
         const float *__restrict__ delta, const float *__restrict__ lse2,
         float *__restrict__ acc_lo, float *__restrict__ acc_hi, Index half_rows,
@@ -296,6 +297,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     int kb, b;                                   // early key blocks see most queries: first
     group_decode(blockIdx.x, nblk, batch, gsz, kb, b);
     const int row_base = b*seq;
+    // K, V, dK, dV may be shared by `kv_group` consecutive groups of `kv_batch`
+    // entries (grouped-query attention on un-replicated K/V; 1 and `batch`
+    // otherwise): the CTAs of a group then add into the same dK / dV tile, which the
+    // element-wise TMA additions of the epilogue allow
+    const int kv_row_base = ((b % kv_batch) + kv_batch*(b/(kv_batch*kv_group)))*seq;
     volatile uint32_t *abort_flag = &sm.abort_flag;
     PROF_DECL;
     PROF_T(c0);
@@ -326,8 +332,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // copies start now, under the set-up of the other warps (a CTA with nothing
         // to do waits for them in the tear-down)
         mbar_arrive_expect_tx(&sm.kv_full, 2*Smem<D>::TILE_BYTES);
-        load_tile<D>(sm.k, &tmap_k, &sm.kv_full, row_base + kb*BLK);
-        load_tile<D>(sm.v, &tmap_v, &sm.kv_full, row_base + kb*BLK);
+        load_tile<D>(sm.k, &tmap_k, &sm.kv_full, kv_row_base + kb*BLK);
+        load_tile<D>(sm.v, &tmap_v, &sm.kv_full, kv_row_base + kb*BLK);
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_g);
         prefetch_tensormap(&tmap_dk);
@@ -897,7 +903,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             __syncwarp();
             if(lane == 0)
             {
-                const int row0 = row_base + kb*BLK + 32*(warp & 3);
+                const int row0 = kv_row_base + kb*BLK + 32*(warp & 3);
 #pragma unroll
                 for(int p = 0; p < PANELS; ++p)
                 {
@@ -985,7 +991,8 @@ bool flash_bwd_sm100_supports(Index seq, Index head, Index batch)
 }
 
 template<int D>
-static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const bf16 *Q,
+static int bwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index kv_batch,
+        const bf16 *K, const bf16 *Q,
         const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask, const float *lse,
         void *scratch_dK, void *scratch_dQ, void *scratch_dV, bf16 *dK, bf16 *dQ, bf16 *dV)
 {
@@ -1010,11 +1017,12 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
         return NNTILE_B200_E_LAUNCH;
     }
     CUtensorMap tk, tv, tq, tg, tdk, tdv;
-    if(!make_tmap_bf16_sw128(&tk, K, rows, D, BLK) || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK)
+    const Index kv_rows = rows/kv_group;
+    if(!make_tmap_bf16_sw128(&tk, K, kv_rows, D, BLK) || !make_tmap_bf16_sw128(&tv, V, kv_rows, D, BLK)
             || !make_tmap_bf16_sw128(&tq, Q, rows, D, BLK)
             || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tdk, dK, rows, D, 32)
-            || !make_tmap_bf16_sw128(&tdv, dV, rows, D, 32))
+            || !make_tmap_bf16_sw128(&tdk, dK, kv_rows, D, 32)
+            || !make_tmap_bf16_sw128(&tdv, dV, kv_rows, D, 32))
     {
         return NNTILE_B200_E_LAUNCH;
     }
@@ -1030,7 +1038,7 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     // Q, K, V, dO, dK, dV (bf16) and the fp32 dQ accumulator of one batch entry
     const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
     flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg, tdk, tdv,
-            (int)seq, (int)batch, gsz, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
+            (int)seq, (int)batch, gsz, (int)kv_group, (int)kv_batch, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
             acc_lo, acc_hi, half_rows, reinterpret_cast<uint32_t *>(sc));
     if(launch_status() != NNTILE_B200_OK)
     {
@@ -1044,13 +1052,17 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
 int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
         const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV, bf16 *dK,
-        bf16 *dQ, bf16 *dV)
+        bf16 *dQ, bf16 *dV, Index kv_group, Index kv_batch)
 {
+    if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0)
+    {
+        return NNTILE_B200_E_BADARG;
+    }
     return head == 128
-            ? bwd_run<128>(s, seq, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scratch_dQ,
-                    scratch_dV, dK, dQ, dV)
-            : bwd_run<64>(s, seq, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scratch_dQ,
-                    scratch_dV, dK, dQ, dV);
+            ? bwd_run<128>(s, seq, batch, kv_group, kv_batch, K, Q, V, A, dA, mask, lse, scratch_dK,
+                    scratch_dQ, scratch_dV, dK, dQ, dV)
+            : bwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, V, A, dA, mask, lse, scratch_dK,
+                    scratch_dQ, scratch_dV, dK, dQ, dV);
 }
 
 } // namespace nb200

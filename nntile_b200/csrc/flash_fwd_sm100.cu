@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
         const __grid_constant__ CUtensorMap tmap_a,
-        int seq, int batch, int gsz, float scale_log2, const bf16 *__restrict__ mask,
+        int seq, int batch, int gsz, int kv_group, int kv_batch, float scale_log2,
+        const bf16 *__restrict__ mask,
         uint8_t *scratch, float *__restrict__ lse, bf16 *__restrict__ A)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -291,6 +292,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int nproc = sm.abort_flag != 0u ? 0 : sm.nproc;
     constexpr uint32_t TILE_BYTES = Smem<D>::TILE_BYTES;
     const int row_base = b*seq;                   // first row of this batch entry
+    // K and V may be shared by `kv_group` consecutive groups of `kv_batch` entries
+    // (grouped-query attention on un-replicated K/V; 1 and `batch` otherwise)
+    const int kv_row_base = ((b % kv_batch) + kv_batch*(b/(kv_batch*kv_group)))*seq;
 
     if(warp < 4)
     {
@@ -310,7 +314,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             {
                 const int st = it % KV_STAGES;
                 const uint32_t ph = (uint32_t)(it/KV_STAGES) & 1u;
-                const int krow = row_base + (int)sm.list[it]*BLK;
+                const int krow = kv_row_base + (int)sm.list[it]*BLK;
                 ok = mbar_wait(&sm.k_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
                 mbar_arrive_expect_tx(&sm.k_full[st], TILE_BYTES);
@@ -817,14 +821,16 @@ bool flash_fwd_sm100_supports(Index seq, Index head, Index batch)
 }
 
 template<int D>
-static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const bf16 *Q,
+static int fwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index kv_batch,
+        const bf16 *K, const bf16 *Q,
         const bf16 *mask, const bf16 *V, float *lse, bf16 *A, uint8_t *scratch)
 {
     using namespace fwd;
     CUtensorMap tq, tk, tv, ta;
     const uint64_t rows = (uint64_t)batch*seq;
-    if(!make_tmap_bf16_sw128(&tq, Q, rows, D, BLK) || !make_tmap_bf16_sw128(&tk, K, rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tv, V, rows, D, BLK)
+    const uint64_t kv_rows = rows/(uint64_t)kv_group;
+    if(!make_tmap_bf16_sw128(&tq, Q, rows, D, BLK) || !make_tmap_bf16_sw128(&tk, K, kv_rows, D, BLK)
+            || !make_tmap_bf16_sw128(&tv, V, kv_rows, D, BLK)
             || !make_tmap_bf16_sw128(&ta, A, rows, D, 32))
     {
         return NNTILE_B200_E_LAUNCH;
@@ -846,7 +852,7 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, const bf16 *K, const 
     // Q, K, V, A of one batch entry
     const int gsz = l2_group_size(batch, (size_t)seq*D*2*4);
     flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, ta, (int)seq, (int)batch, gsz,
-            scale_log2, mask, scratch, lse, A);
+            (int)kv_group, (int)kv_batch, scale_log2, mask, scratch, lse, A);
     return launch_status();
 }
 
@@ -859,8 +865,12 @@ int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *scr
 
 int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A, void *scratch,
-        size_t scratch_bytes)
+        size_t scratch_bytes, Index kv_group, Index kv_batch)
 {
+    if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0)
+    {
+        return NNTILE_B200_E_BADARG;
+    }
     const size_t nblk = (size_t)(seq/fwd::BLK);
     if(scratch_bytes < CLS_OFFSET + nblk*nblk)
     {
@@ -868,8 +878,8 @@ int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf
     }
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     return head == 128
-            ? fwd_run<128>(s, seq, batch, K, Q, mask, V, lse, A, sc)
-            : fwd_run<64>(s, seq, batch, K, Q, mask, V, lse, A, sc);
+            ? fwd_run<128>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, sc)
+            : fwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, sc);
 }
 
 } // namespace nb200

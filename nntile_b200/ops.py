@@ -132,6 +132,25 @@ def flash_sdpa_bwd(seq, head, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scra
           _ptr(scratch_dQ), _ptr(scratch_dV), _ptr(dK), _ptr(dQ), _ptr(dV))
 
 
+def flash_sdpa_gqa_scratch_bytes(seq, head, batch, group, kv_heads) -> int:
+    return int(_lib.load().nntile_b200_flash_sdpa_gqa_scratch_bytes(seq, head, batch, group,
+                                                                    kv_heads))
+
+
+def flash_sdpa_fwd_gqa(seq, head, batch, group, kv_heads, K, Q, mask, V, lse, A, scratch):
+    """K, V un-replicated [head, seq, batch, kv_heads]; Q, A with the group index."""
+    _call("nntile_b200_flash_sdpa_fwd_gqa_bf16", _stream(), seq, head, batch, group, kv_heads,
+          _ptr(K), _ptr(Q), _ptr(mask), _ptr(V), _ptr(lse), _ptr(A), _ptr(scratch),
+          scratch.numel()*scratch.element_size())
+
+
+def flash_sdpa_bwd_gqa(seq, head, batch, group, kv_heads, K, Q, V, A, dA, mask, lse, dK, dQ, dV,
+                       scratch):
+    _call("nntile_b200_flash_sdpa_bwd_gqa_bf16", _stream(), seq, head, batch, group, kv_heads,
+          _ptr(K), _ptr(Q), _ptr(V), _ptr(A), _ptr(dA), _ptr(mask), _ptr(lse), _ptr(dK),
+          _ptr(dQ), _ptr(dV), _ptr(scratch), scratch.numel()*scratch.element_size())
+
+
 def flash_sdpa_path(seq, head, batch, backward=False) -> int:
     lib = _lib.load()
     fn = lib.nntile_b200_flash_sdpa_bwd_path if backward else lib.nntile_b200_flash_sdpa_fwd_path

@@ -231,3 +231,66 @@ def test_forward_merges_into_existing_partial_result():
     got = O.from_bf16(to_fortran(A.view(1, 1, batch, seq, head)))
     assert O.rel_err(got, a64) <= 1e-2
     assert np.allclose(lse.cpu().numpy().T, l64[:, :, 0, 0], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("head,seq,batch,group,kvh,kind", [
+    (128, 256, 2, 4, 2, "causal"),
+    (64, 384, 1, 3, 2, "ragged"),
+    (128, 128, 3, 2, 1, "none"),
+])
+def test_grouped_query_entry_points(head, seq, batch, group, kvh, kind):
+    """Native GQA: K, V un-replicated.  Oracle = the reference's way: replicate K/V
+    over the group (llama_attention.py:605-616), run the tile tasks, sum dK/dV over
+    the group (:786-793)."""
+    rng = np.random.default_rng(head + seq + group)
+    qshape, kshape = (head, seq, batch, group, kvh), (head, seq, batch, kvh)
+    Q, dA = (O.to_bf16(rng.standard_normal(qshape).astype(np.float32)) for _ in range(2))
+    Kkv, Vkv = (O.to_bf16(rng.standard_normal(kshape).astype(np.float32)) for _ in range(2))
+    Krep = F(np.repeat(Kkv[:, :, :, None, :], group, axis=3))
+    Vrep = F(np.repeat(Vkv[:, :, :, None, :], group, axis=3))
+    mask = O.to_bf16(make_mask(kind, seq))
+    wantA, wantL = O.flash_forward(Q, Krep, Vrep, mask)
+    fin = np.isfinite(wantL)
+    q, k, v, m = dev(Q), dev(Kkv), dev(Vkv), dev(mask)
+    lse = torch.full((kvh, group, batch, seq), -np.inf, dtype=torch.float32, device="cuda")
+    A = torch.zeros_like(q)
+    nbytes = ops.flash_sdpa_gqa_scratch_bytes(seq, head, batch, group, kvh)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    ops.flash_sdpa_fwd_gqa(seq, head, batch, group, kvh, k, q, m, v, lse, A, scratch)
+    torch.cuda.synchronize()
+    assert O.rel_err(bf(A), O.from_bf16(wantA)) <= BF16_TOL
+    gl = to_fortran(lse)
+    assert np.array_equal(np.isfinite(gl), fin)
+    assert np.allclose(gl[fin], wantL[fin], rtol=1e-3, atol=1e-3)
+    # backward from the oracle's A and lse; dK, dV start from a non-zero value ("+=")
+    z = lambda: O.zeros(qshape, np.uint16)
+    lse_in = F(np.where(fin, wantL, 0.0).astype(np.float32))
+    wq, wk, wv = O.flash_backward(Q, Krep, Vrep, wantA, dA, mask, lse_in, z(), z(), z())
+    wk_kv = O.from_bf16(wk).sum(axis=3) + 0.5
+    wv_kv = O.from_bf16(wv).sum(axis=3) + 0.5
+    dQ = torch.zeros_like(q)
+    dK = torch.full(tuple(reversed(kshape)), 0.5, dtype=torch.bfloat16, device="cuda")
+    dV = torch.full_like(dK, 0.5)
+    ops.flash_sdpa_bwd_gqa(seq, head, batch, group, kvh, k, q, v, dev(wantA), dev(dA), m,
+                           dev(lse_in), dK, dQ, dV, scratch)
+    torch.cuda.synchronize()
+    assert O.rel_err(bf(dQ), O.from_bf16(wq)) <= BF16_TOL
+    assert O.rel_err(bf(dK), wk_kv) <= BF16_TOL
+    assert O.rel_err(bf(dV), wv_kv) <= BF16_TOL
+    # inputs untouched
+    assert np.array_equal(to_fortran(k), Kkv) and np.array_equal(to_fortran(v), Vkv)
+
+
+def test_grouped_query_rejects_unsupported_shape_and_small_scratch():
+    from nntile_b200 import _lib
+    t = lambda *s: torch.zeros(s, dtype=torch.bfloat16, device="cuda")
+    q, k = t(1, 2, 1, 80, 32), t(1, 1, 80, 32)
+    lse = torch.zeros((1, 2, 1, 80), dtype=torch.float32, device="cuda")
+    sc = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    with pytest.raises(_lib.StatusError):      # seq 80, head 32: no tcgen05 kernel
+        ops.flash_sdpa_fwd_gqa(80, 32, 1, 2, 1, k, q, t(80, 80), k, lse, q, sc)
+    q, k = t(1, 2, 1, 128, 128), t(1, 1, 128, 128)
+    lse = torch.zeros((1, 2, 1, 128), dtype=torch.float32, device="cuda")
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    with pytest.raises(_lib.StatusError):
+        ops.flash_sdpa_bwd_gqa(128, 128, 1, 2, 1, k, q, k, q, q, t(128, 128), lse, k, q, k, small)
