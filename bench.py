@@ -519,12 +519,45 @@ def run_extras(torch, ops, lib, dev, peaks, args):
     del wl
     # ---- config 4: long context, seq-tile 2048, K/V tiles streamed through tasks
     out["c4_long_context"] = run_c4(torch, ops, lib, dev, steps)
+    # ---- config 3 through the grouped-query entry points (K, V not replicated)
+    out["c3_native_gqa"] = run_c3_gqa(torch, ops, dev, steps)
     # ---- config 5: decode, HBM-bound
     out["c5_decode"] = run_decode(torch, ops, dev, peaks, C5, steps*4, 5)
     # ---- library comparator (context only, not the product): cuDNN's SDPA as the
     # reference reaches it - additive bf16 bias, no causal flag - and with the flag
     out["cudnn_comparator_c3"] = run_cudnn_comparator(torch, dev)
     return out
+
+
+def run_c3_gqa(torch, ops, dev, steps):
+    """Config 3 with K, V, dK, dV of shape [head, seq, batch, kv_heads]: the same tile
+    task without the reference layer's K/V replication and gradient reduction."""
+    cfg = C3
+    H, G, B, S, D = cfg["kv_heads"], cfg["group"], cfg["batch"], cfg["seq"], cfg["head"]
+    g = torch.Generator(device=dev).manual_seed(7)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev).to(torch.bfloat16)
+    q, dy = rnd(H, G, B, S, D), rnd(H, G, B, S, D)
+    k, v = rnd(H, B, S, D), rnd(H, B, S, D)
+    rope_(q)
+    rope_(k.view(H, 1, B, S, D))
+    mask = causal_mask_tile(S, "diag", dev)
+    y, dq = torch.zeros_like(q), torch.zeros_like(q)
+    dk, dv = torch.zeros_like(k), torch.zeros_like(k)
+    lse = torch.empty((H, G, B, S), dtype=torch.float32, device=dev)
+    scratch = torch.empty(ops.flash_sdpa_gqa_scratch_bytes(S, D, B, G, H), dtype=torch.uint8,
+                          device=dev)
+
+    def step():
+        ops.fill(-math.inf, lse)
+        ops.clear(y)
+        ops.flash_sdpa_fwd_gqa(S, D, B, G, H, k, q, mask, v, lse, y, scratch)
+        ops.flash_sdpa_bwd_gqa(S, D, B, G, H, k, q, v, y, dy, mask, lse, dk, dq, dv, scratch)
+
+    ms, _, _ = time_steps(torch, step, steps, 3)
+    ms /= steps
+    f, b = causal_flops(cfg)
+    return {"tflops": (f + b)/(ms*1e-3)/1e12, "ms_per_step": ms,
+            "note": "K, V, dK, dV [head, seq, batch, kv_heads]; same FLOPs as the headline"}
 
 
 def run_cudnn_comparator(torch, dev):
