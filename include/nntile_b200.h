@@ -258,8 +258,12 @@ size_t nntile_b200_decode_sdpa_noalloc_max_bytes(void);
  * order of the tile grid.  mask is [seq, seq] tiled [basetile[1], basetile[1]]
  * (tile (k, q) at k + q*nseq_tiles), lse is [seq, batch, group, kv_heads] tiled
  * like A without the head axis.  For every output tile, one tile task per K/V
- * sequence tile is enqueued in order (fully masked pairs included, as in the
- * reference).  The caller runs the prologue (lse = -inf, A = 0) for the forward
+ * sequence tile is enqueued in order, fully masked pairs included, as in the
+ * reference - unless the caller says otherwise: a NULL entry in `mask_tiles` marks
+ * its (K/V tile, Q tile) pair as fully masked and no task is generated for it
+ * (under a causal mask 44 % of the pairs of config 4), and several entries may point
+ * to the same buffer, so a causal mask needs one zero tile and one diagonal tile
+ * instead of a dense [seq, seq] tensor.  The caller runs the prologue (lse = -inf, A = 0) for the forward
  * and provides `scratch` of nntile_b200_tensor_flash_sdpa_scratch_bytes(basetile)
  * bytes, 256-byte aligned, reused by every task.
  * Replace nntile::tensor::flash_sdpa_fwd_cudnn_async<bf16_t>,

@@ -85,6 +85,10 @@ extern "C" int nntile_b200_tensor_flash_sdpa_fwd_bf16(nntile_b200_stream_t strea
             {
                 return NNTILE_B200_E_SHAPE;   // "K tile sequence length mismatches Q tile"
             }
+            if(!mask_tiles[ki + qi*nseq])
+            {
+                continue;   // the caller marked this pair as fully masked: no task
+            }
             const Index kv = a + (ki - qi)*g.grid[0];
             const int st = nntile_b200_flash_sdpa_fwd_bf16(stream, seq_q, g.shape[0], batch,
                     K_tiles[kv], Q_tiles[a], mask_tiles[ki + qi*nseq], scratch_lse,
@@ -129,6 +133,10 @@ extern "C" int nntile_b200_tensor_flash_sdpa_bwd_bf16(nntile_b200_stream_t strea
         for(Index ki = 0; ki < nseq; ++ki)
         {
             if(extent(g, 1, ki) != seq_q) return NNTILE_B200_E_SHAPE;
+            if(!mask_tiles[ki + qi*nseq])
+            {
+                continue;   // fully masked pair: contributes nothing to any gradient
+            }
             const Index kv = a + (ki - qi)*g.grid[0];
             const int st = nntile_b200_flash_sdpa_bwd_bf16(stream, seq_q, g.shape[0], batch,
                     K_tiles[kv], Q_tiles[a], V_tiles[kv], A_tiles[a], dA_tiles[a],

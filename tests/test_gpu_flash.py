@@ -294,3 +294,45 @@ def test_grouped_query_rejects_unsupported_shape_and_small_scratch():
     small = torch.empty(1024, dtype=torch.uint8, device="cuda")
     with pytest.raises(_lib.StatusError):
         ops.flash_sdpa_bwd_gqa(128, 128, 1, 2, 1, k, q, k, q, q, t(128, 128), lse, k, q, k, small)
+
+
+def test_null_mask_tile_skips_the_pair():
+    """Tensor level: a NULL mask entry = fully masked pair, no task; the result is
+    the one with every pair submitted and shared zero / diagonal / -inf tiles."""
+    import ctypes
+    from nntile_b200 import _lib
+    lib = _lib.load()
+    D, S, St, H = 64, 512, 128, 3
+    nt = S//St
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rnd = lambda: [torch.randn((H, 1, 1, St, D), generator=g, device="cuda").to(torch.bfloat16)
+                   for _ in range(nt)]
+    Q, K, V, dY = rnd(), rnd(), rnd(), rnd()
+    mz = dev(O.to_bf16(F(np.zeros((St, St), np.float32))))
+    md = dev(O.to_bf16(causal_add(St)))
+    mi = dev(O.to_bf16(F(np.full((St, St), -np.inf, np.float32))))
+    i64 = ctypes.c_int64
+    shape, base = (i64*5)(D, S, 1, 1, H), (i64*5)(D, St, 1, 1, H)
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(base)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    parr = lambda ps: ctypes.cast((ctypes.c_void_p*len(ps))(*ps), ctypes.POINTER(ctypes.c_void_p))
+    ptrs = lambda ts: parr([t.data_ptr() for t in ts])
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    results = []
+    for skip in (False, True):
+        mp = [(0 if skip else mi.data_ptr()) if ki > qi else (mz if ki < qi else md).data_ptr()
+              for qi in range(nt) for ki in range(nt)]
+        A = [torch.zeros_like(q) for q in Q]
+        lse = [torch.full((H, 1, 1, St), -np.inf, dtype=torch.float32, device="cuda") for _ in Q]
+        dQ, dK, dV = ([torch.zeros_like(q) for q in Q] for _ in range(3))
+        st = lib.nntile_b200_tensor_flash_sdpa_fwd_bf16(stream, shape, base, ptrs(K), ptrs(Q),
+                parr(mp), ptrs(lse), ptrs(V), ptrs(A), ctypes.c_void_p(scratch.data_ptr()), nbytes)
+        assert st == 0
+        st = lib.nntile_b200_tensor_flash_sdpa_bwd_bf16(stream, shape, base, ptrs(K), ptrs(Q),
+                ptrs(V), ptrs(A), ptrs(dY), parr(mp), ptrs(lse), ptrs(dK), ptrs(dQ), ptrs(dV),
+                ctypes.c_void_p(scratch.data_ptr()), nbytes)
+        assert st == 0
+        torch.cuda.synchronize()
+        results.append([torch.stack(x) for x in (A, lse, dQ, dK, dV)])
+    for full, skipped in zip(*results):
+        assert torch.equal(full, skipped)       # a fully masked task changes nothing
