@@ -756,16 +756,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                              : fmaf(bias, LOG2E_F, x[u]);
                             }
                         }
-                        // half of the exponentials on the MUFU unit, half as a cubic on
-                        // the FMA pipe: 16384 ex2 per block pair would otherwise hold
-                        // the 16-per-clock unit for as long as two of the five MMAs
-                        float e2, e3;
-#ifdef NB200_BWD_POLY_EXP
-                        unpack_f32x2(ex2_poly2(pack_f32x2(x[2], x[3])), e2, e3);
-#else
-                        e2 = ex2(x[2]);
-                        e3 = ex2(x[3]);
-#endif
+                        // all four on the MUFU unit: a cubic on the FMA pipe for part of
+                        // them was measured slower (the warps are short of issue slots)
+                        const float e2 = ex2(x[2]), e3 = ex2(x[3]);
                         pk[c2][j >> 1] = pack_bf16x2(ex2(x[0]), ex2(x[1]));
                         pk[c2][(j >> 1) + 1] = pack_bf16x2(e2, e3);
                     }

@@ -468,32 +468,6 @@ __device__ __forceinline__ float ex2(float x)
     return y;
 }
 
-// exp2 of two packed fp32 values on the FMA and ALU pipes, for when the MUFU unit
-// (16 ex2 per clock per SM) is the limiter: round to the nearest integer n with
-// the 1.5*2^23 trick, a cubic for 2^f on f in [-0.5, 0.5] (relative error 1e-4,
-// well below the bf16 rounding of the probabilities), then n is added into the
-// exponent field.  Inputs below -126 (including -inf) give a value <= 2^-126.
-__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2)
-{
-    float x0, x1;
-    unpack_f32x2(x2, x0, x1);
-    x2 = pack_f32x2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-    const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);
-    const uint64_t t2 = fadd2(x2, magic);
-    const uint64_t n2 = fadd2(t2, pack_f32x2(-12582912.0f, -12582912.0f));
-    const uint64_t f2 = ffma2(n2, pack_f32x2(-1.0f, -1.0f), x2);
-    uint64_t p2 = ffma2(pack_f32x2(0.05583828f, 0.05583828f), f2,
-            pack_f32x2(0.24263948f, 0.24263948f));
-    p2 = ffma2(p2, f2, pack_f32x2(0.69313675f, 0.69313675f));
-    p2 = ffma2(p2, f2, pack_f32x2(0.99992454f, 0.99992454f));
-    float p0, p1, t0, t1;
-    unpack_f32x2(p2, p0, p1);
-    unpack_f32x2(t2, t0, t1);
-    p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-    return pack_f32x2(p0, p1);
-}
-
 } // namespace sm100
 
 // ----------------------------------------------------------- host: tensor maps
