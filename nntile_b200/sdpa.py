@@ -185,6 +185,40 @@ class Sdpa:
         ops.gemm(False, False, D, Sq, Sk, nb, 1.0, self.v, self.attn, 0.0, self.y)
         return self.y
 
+    def forward_dynamic(self, q, k, v, mask=None, kv_cache=None):
+        """nntile.layer.Sdpa.forward_dynamic (sdpa.py:170-306): forward on tensors
+        handed in at call time - the key/value sequence may be longer than the query
+        sequence (generation against a cache) - with temporaries allocated on the
+        fly; no backward.  As there, the fused path runs only when the two sequence
+        lengths agree; otherwise the unfused chain.  ``mask`` is what the
+        constructor takes for the chosen path.
+
+        Beyond the reference: with ``kv_cache`` (a KVCache holding the un-replicated
+        keys and values) and a single query position, the split-KV decode kernel
+        reads the filled part of the cache in place; k and v are then ignored."""
+        H, G, B, Sq, D = q.shape
+        if kv_cache is not None and Sq == 1 and len(kv_cache) > 0:
+            return kv_cache.decode(q)
+        Sk = k.shape[3]
+        mask_local = mask if mask is not None else self.mask
+        y = torch.zeros_like(q)
+        nb = H*G*B
+        if self.flash_attention and Sk == Sq:
+            lse = torch.full((H, G, B, Sq), -math.inf, dtype=torch.float32, device=q.device)
+            if mask_local is None:
+                mask_local = torch.zeros((Sq, Sq), dtype=q.dtype, device=q.device)
+            flash_sdpa_fwd_async(k, q, mask_local, lse, v, y, self.seq_tile, self.batch_tile)
+            return y
+        attn = torch.empty((H, G, B, Sq, Sk), dtype=q.dtype, device=q.device)
+        attn_max = torch.zeros((H, G, B, Sq, 2), dtype=q.dtype, device=q.device)
+        ops.gemm(True, False, Sk, Sq, D, nb, sdpa_scale(D), k, q, 0.0, attn)
+        if mask_local is not None:
+            ops.mask_scalar(Sk*Sq, nb, mask_local, self.val, attn)
+        ops.maxsumexp(1, Sq*nb, Sk, attn, attn_max)
+        ops.softmax_inplace(1, Sq*nb, Sk, attn_max, 1.0, attn)
+        ops.gemm(False, False, D, Sq, Sk, nb, 1.0, v, attn, 0.0, y)
+        return y
+
     # ---- backward: dq, dk, dv are INCREMENTED, as in the reference -----------
     def backward_async(self, dy, dq, dk, dv):
         if self.flash_attention:

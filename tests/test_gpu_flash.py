@@ -336,3 +336,43 @@ def test_null_mask_tile_skips_the_pair():
         results.append([torch.stack(x) for x in (A, lse, dQ, dK, dV)])
     for full, skipped in zip(*results):
         assert torch.equal(full, skipped)       # a fully masked task changes nothing
+
+
+def test_layer_forward_dynamic_prefill_then_decode():
+    """Sdpa.forward_dynamic: fused path when the sequence lengths agree, the
+    unfused chain against a longer key/value sequence, and the decode kernel on a
+    KVCache - all against the oracle's unfused chain (sdpa.py:170-306)."""
+    from nntile_b200.sdpa import KVCache
+    rng = np.random.default_rng(8)
+    D, S, B, G, H = 64, 128, 2, 2, 1
+    shape = (D, S, B, G, H)
+    Q, K, V = (O.to_bf16(F(rng.standard_normal(shape).astype(np.float32))) for _ in range(3))
+    layer = Sdpa(dev(Q), dev(K), dev(V), mask=dev(O.to_bf16(causal_add(S))),
+                 flash_attention=True)
+    maskb = F(np.triu(np.ones((S, S), dtype=bool)))
+    want, _, _ = O.vanilla_forward(O.from_bf16(Q), O.from_bf16(K), O.from_bf16(V), maskb)
+    y = layer.forward_dynamic(dev(Q), dev(K), dev(V))
+    torch.cuda.synchronize()
+    assert O.rel_err(bf(y), want) <= BF16_TOL
+    # one new query against S + 1 keys: unfused chain, no mask
+    q1 = O.to_bf16(F(rng.standard_normal((D, 1, B, G, H)).astype(np.float32)))
+    k1, v1 = (O.to_bf16(F(rng.standard_normal((D, 1, B, G, H)).astype(np.float32)))
+              for _ in range(2))
+    Kall, Vall = F(np.concatenate([K, k1], axis=1)), F(np.concatenate([V, v1], axis=1))
+    want1, _, _ = O.vanilla_forward(O.from_bf16(q1), O.from_bf16(Kall), O.from_bf16(Vall), None)
+    plain = Sdpa(dev(Q), dev(K), dev(V), flash_attention=False)
+    y1 = plain.forward_dynamic(dev(q1), dev(Kall), dev(Vall))
+    torch.cuda.synchronize()
+    assert O.rel_err(bf(y1), want1) <= BF16_TOL
+    # the same step on an un-replicated cache (group 2 shares one kv head here only if
+    # the replicas are equal: build K/V with equal group entries)
+    Kkv = F(Kall[:, :, :, 0, :])
+    Vkv = F(Vall[:, :, :, 0, :])
+    Krep = F(np.repeat(Kkv[:, :, :, None, :], G, axis=3))
+    Vrep = F(np.repeat(Vkv[:, :, :, None, :], G, axis=3))
+    want2, _, _ = O.vanilla_forward(O.from_bf16(q1), O.from_bf16(Krep), O.from_bf16(Vrep), None)
+    cache = KVCache(256, H, B, D)
+    cache.append(dev(Kkv), dev(Vkv))
+    y2 = layer.forward_dynamic(dev(q1), None, None, kv_cache=cache)
+    torch.cuda.synchronize()
+    assert O.rel_err(bf(y2), want2) <= BF16_TOL
