@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) building blocks as inline PTX: mbarriers with BOUNDED
-// waits, TMA tiled loads (no multicast anywhere), tensor-memory management and
+// waits, TMA tiled loads (every copy targets this CTA only), tensor-memory management and
 // the tcgen05 MMA / load / store instructions with their descriptors.
 #pragma once
 
