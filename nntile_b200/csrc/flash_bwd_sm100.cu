@@ -388,12 +388,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
     if(warp < 4)
     {
-    // control warpgroup: hand registers to the drain warpgroup, which then holds a
-    // whole dQ_i tile (128 columns) and frees the TMEM columns after one load round.
-    // An increase is only ever served from registers a warpgroup of this CTA gave
-    // up, and waits for them without a bound, so released must equal requested:
-    // launch 128 x 512 = control 96 x 128 + drain 160 x 128 + softmax 128 x 256.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    // control warpgroup: hand registers to the drain warpgroup, which holds a whole
+    // dQ_i tile (128 columns) and frees the TMEM columns after one load round, and to
+    // the softmax warpgroups.  An increase is only ever served from registers a
+    // warpgroup of this CTA gave up, and waits for them without a bound, so released
+    // must equal requested: launch 128 x 512 = control 80 x 128 + drain 144 x 128 +
+    // softmax 144 x 256.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
     if(warp == 0)
     {
         // =============================== TMA producer ==========================
@@ -596,7 +597,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     else if(warp < 8)
     {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 144;");
         // ================================ dQ drain =============================
         const int r = 32*(warp & 3) + lane;
         const uint32_t src = dq_tm + ((uint32_t)(32*(warp & 3)) << 16);
@@ -689,6 +690,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     else
     {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 144;");
         // ================================= softmax =============================
         const int ts = tid - 256;                     // 0..255
         const int h = ts >> 7;                        // query-column half
