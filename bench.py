@@ -131,9 +131,12 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = sorted(sm)[len(sm)//2:]          # upper half = samples under load
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx),
-                "power_w_max": max(pw), "samples": len(sm), "reasons": sorted(reasons)}
+        # samples under load = those drawing most of the peak power seen (an idle GPU
+        # clocks down, a power-capped busy one clocks down too: power tells them apart)
+        busy = [c for c, w in zip(sm, pw) if w >= 0.6*max(pw)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_mhz_min_under_load": min(busy),
+                "sm_max_mhz": max(mx), "power_w_max": max(pw), "samples": len(sm),
+                "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------------
