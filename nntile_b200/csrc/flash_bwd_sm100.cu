@@ -33,8 +33,14 @@
 // warps waits behind them, so the drain issues four at a time on a clock schedule
 // just below that rate.
 //
-// 512 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 dQ drain,
-// warps 8-15 softmax (two warps per TMEM lane quarter, 64 query columns each).
+// 512 threads: warp 0 TMA producer (K/V right at the start, then Q/dO with the
+// softmax statistics through a 2-stage ring), warp 1 MMA issuer, warps 4-7 dQ
+// drain, warps 8-15 softmax (two warps per TMEM lane quarter, 64 query columns
+// each); during the set-up warp 2 reads the status word and warp 3 compacts the
+// class table into the list of query blocks to walk.  dK and dV leave through
+// shared memory as TMA element-wise additions ("+=" without reading the old
+// values), which is also what lets several CTAs share a dK/dV tile in the
+// grouped-query form.
 //
 // The fp32 dQ accumulator, delta = rowsum(A o dA), lse*log2(e) and the mask
 // class table live in the three scratch buffers the reference's tile layer

@@ -11,8 +11,9 @@
 // (one (batch, head) slice) and walks the 128-key blocks that at least one of
 // them needs.  384 threads (three warpgroups) in three roles; the control
 // warpgroup hands most of its registers to the softmax warpgroups (setmaxnreg):
-//   warp 0      TMA producer: Q tiles once, then K and V blocks through two
-//               2-stage rings (64-column panels, 128-byte swizzle)
+//   warp 0      TMA producer: the two Q tiles right at the start (before the
+//               block list exists), then K and V blocks through two 2-stage
+//               rings (64-column panels, 128-byte swizzle)
 //   warp 1      MMA issuer: S_t = Q_t K^T (operands in shared memory) and
 //               O_t += P_t V (P_t read from TMEM, V MN-major from shared memory);
 //               owns the TMEM allocation (512 columns: S_0 S_1 O_0 O_1)
@@ -20,7 +21,10 @@
 //               per query row: tcgen05.ld of the S row, bias, running max with a
 //               lazy rescale of O (only when the max grows by more than 2^8),
 //               exp2, bf16 P written back into the S columns, and at the end the
-//               normalisation, the merge with the stored (lse, A) and the store.
+//               normalisation, the merge with the stored (lse, A) and the store
+//               (staged through shared memory; a TMA store when nothing is merged).
+// During the set-up warp 1 allocates TMEM, warp 2 reads the status word and
+// warp 3 compacts the class table into the list of key blocks to walk.
 // While one group is busy with exponentials the tensor pipe works for the other
 // tile (PV_0, QK_0', PV_1, QK_1' ...), so MUFU and MMA overlap.
 //
