@@ -465,6 +465,13 @@ def run_gpu_arm(args):
     e2e = {"value": world*flops_step/(e2e_ms*1e-3)/1e12, "unit": UNIT, "ms_per_step": e2e_ms,
            "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     del host_in, host_out
+    if world == 1:
+        # the same step through the grouped-query entry points: the host holds K, V
+        # (and receives dK, dV) per kv head, not replicated over the group
+        try:
+            e2e["grouped_query_api"] = run_e2e_gqa(torch, ops, dev, cfg, flops_step, e2e_steps)
+        except Exception as ex:                      # informational; never breaks the line
+            e2e["grouped_query_api"] = {"error": repr(ex)}
 
     extra, cpu_baseline = None, None
     if world == 1:
@@ -530,6 +537,43 @@ def run_extras(torch, ops, lib, dev, peaks, args):
     # reference reaches it - additive bf16 bias, no causal flag - and with the flag
     out["cudnn_comparator_c3"] = run_cudnn_comparator(torch, dev)
     return out
+
+
+def run_e2e_gqa(torch, ops, dev, cfg, flops_step, steps):
+    """End-to-end step with pinned host buffers through the grouped-query entry
+    points, copies overlapped with kernels by HostStream (chunks of one kv head)."""
+    from nntile_b200.parallel import HostStream
+    H, G, B, S, D = cfg["kv_heads"], cfg["group"], cfg["batch"], cfg["seq"], cfg["head"]
+    g = torch.Generator(device=dev).manual_seed(11)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev).to(torch.bfloat16)
+    q, dy, k, v = rnd(H, G, B, S, D), rnd(H, G, B, S, D), rnd(H, B, S, D), rnd(H, B, S, D)
+    y, dq = torch.zeros_like(q), torch.zeros_like(q)
+    dk, dv = torch.zeros_like(k), torch.zeros_like(k)
+    lse = torch.empty((H, G, B, S), dtype=torch.float32, device=dev)
+    mask = causal_mask_tile(S, "diag", dev)
+    scratch = torch.empty(ops.flash_sdpa_gqa_scratch_bytes(S, D, B, G, 1), dtype=torch.uint8,
+                          device=dev)
+
+    def body(lo, hi):
+        n = hi - lo
+        ops.fill(-math.inf, lse[lo:hi])
+        ops.clear(y[lo:hi])
+        ops.flash_sdpa_fwd_gqa(S, D, B, G, n, k[lo:hi], q[lo:hi], mask, v[lo:hi], lse[lo:hi],
+                               y[lo:hi], scratch)
+        ops.flash_sdpa_bwd_gqa(S, D, B, G, n, k[lo:hi], q[lo:hi], v[lo:hi], y[lo:hi], dy[lo:hi],
+                               mask, lse[lo:hi], dk[lo:hi], dq[lo:hi], dv[lo:hi], scratch)
+
+    host_in = [x.cpu().pin_memory() for x in (q, k, v, dy)]
+    host_out = [torch.empty_like(x, device="cpu").pin_memory() for x in (y, dq, dk, dv)]
+    pipe = HostStream(dev, H, chunks=H)
+    step = lambda: pipe.step(host_in, (q, k, v, dy), body, (y, dq, dk, dv), host_out)
+    ms, _, _ = time_steps(torch, step, steps, 1)
+    ms /= steps
+    return {"value": flops_step/(ms*1e-3)/1e12, "unit": UNIT, "ms_per_step": ms,
+            "h2d_bytes_per_step": sum(x.numel()*x.element_size() for x in host_in),
+            "d2h_bytes_per_step": sum(x.numel()*x.element_size() for x in host_out),
+            "note": "K, V, dK, dV [head, seq, batch, kv_heads]: a quarter of the K/V bytes "
+                    "cross PCIe; same FLOPs as the headline"}
 
 
 def run_c3_gqa(torch, ops, dev, steps):
