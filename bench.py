@@ -61,7 +61,7 @@ C5 = dict(head=128, max_seq=8192, batch=64, group=4, kv_heads=8)
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch, one-pass capture
 # of the full 128-slice workload; slices are independent, so a launch on fewer
 # slices moves proportionally less)
-NCU_DRAM_BYTES_PER_SLICE = {"flash_bwd_kernel<128>": 1569.0e6/128, "flash_fwd_kernel<128>": 519.0e6/128}
+NCU_DRAM_BYTES_PER_SLICE = {"flash_bwd_kernel<128>": 1563.0e6/128, "flash_fwd_kernel<128>": 519.0e6/128}
 
 
 def causal_flops(cfg):
