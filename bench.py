@@ -11,19 +11,24 @@ flash-SDPA tile tasks over one batch of synthetic input, per GPU):
   RoPE (base 10000) pre-applied to Q and K ~ N(0,1), dY ~ N(0,1); one sequence
   tile (seq-tile 4096), all calls through the C ABI of include/nntile_b200.h.
 The metric is TFLOP/s under the causal convention (forward 2W, backward 5W,
-W = B*Hq*S^2*D).  Scaling is weak: every rank runs the same per-GPU workload on
-its own shard of independent (batch, kv head) units; there is no collective on
-the data path.
+W = B*Hq*S^2*D).  Scaling is strong: config 3 is ONE problem of 32 independent
+(batch, kv head) units; with N GPUs every rank takes the block of 8/N kv heads
+that nntile_b200.parallel.shard_range deals it (what the reference does by
+placing tile tasks on N StarPU CUDA workers), `value` is the FLOPs of the whole
+problem over the slowest rank's time, and there is no collective on the data
+path.  (`extra.weak_scaling`, N > 1 only: every rank runs all of config 3.)
 
 The single JSON line also carries: `roofline` (dominant kernel = the backward
-tile task, timed live with CUDA events, against the measured sustained bf16
-GEMM rate of MEASURED_PEAKS.json), `cpu_baseline` (the reference's own CPU
+tile task, timed live with CUDA events, against the measured bf16 GEMM rates of
+MEASURED_PEAKS.json - burst or sustained by the rule in roofline_regime()),
+`cpu_baseline` (the reference's own CPU
 kernels timed on a bounded sample, rank 0, N=1), `e2e` (same metric through the
 same C-ABI calls with HOST buffers: pinned host -> device copies of Q, K, V, dY
 and device -> host reads of A, dQ, dK, dV inside the timed region), `clocks`
 (nvidia-smi samples taken during the timed region), `gpu_launches` (kernels of
 this library launched in the timed region, from the library's own counter) and
-`extra` (N=1 only: configs 2, 4 and the decode config 5 in GB/s vs HBM peak).
+`extra` (configs 2, 4, the layout-change kernels and library comparators at N=1;
+the decode config 5, its batch split over the ranks, in GB/s vs HBM peak at every N).
 
 `--impl reference` times the reference's CPU implementation of the path (its own
 src/kernel/*/cpu.cc + OpenBLAS sgemm, compiled in place as oracle/_ref; the C
@@ -62,6 +67,10 @@ C5 = dict(head=128, max_seq=8192, batch=64, group=4, kv_heads=8)
 # of the full 128-slice workload; slices are independent, so a launch on fewer
 # slices moves proportionally less)
 NCU_DRAM_BYTES_PER_SLICE = {"flash_bwd_kernel<128>": 1563.0e6/128, "flash_fwd_kernel<128>": 519.0e6/128}
+# share of the backward tile task's device time spent in flash_bwd_kernel<128> itself
+# (the rest: mask classification, delta / accumulator preparation, dQ conversion), from
+# the ncu launch list of the config-3 workload (profiles/)
+NCU_BWD_KERNEL_SHARE = 0.895
 
 
 def causal_flops(cfg):
@@ -73,9 +82,23 @@ def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return dict(bf16=d.get("bf16_tflops_sustained", 1400.0), bf16_burst=d.get("bf16_tflops"),
-                    hbm=d.get("hbm_gbs", 6650.0), source="measured")
-    return dict(bf16=1400.0, bf16_burst=1590.0, hbm=6650.0, source="fallback")
+        return dict(bf16=d.get("bf16_tflops_sustained", 1400.0),
+                    bf16_burst=d.get("bf16_tflops", 1590.0), hbm=d.get("hbm_gbs", 6650.0),
+                    sustained_mhz=(d.get("clocks_under_load") or {}).get("sm_mhz_median", 1275.0),
+                    source="measured")
+    return dict(bf16=1400.0, bf16_burst=1590.0, hbm=6650.0, sustained_mhz=1300.0,
+                source="fallback")
+
+
+def roofline_regime(peaks, timed_ms, sm_mhz):
+    """Which measured GEMM rate a fraction is taken against.  The sustained rate was
+    measured in a seconds-long loop with the board at its power limit and the SM
+    clock far below maximum; the burst rate in a short run at full clock.  A timed
+    region shorter than a second, or one whose sampled median SM clock is above the
+    clock at which the sustained rate was measured, is in the burst regime."""
+    if timed_ms < 1000.0 or (sm_mhz is not None and sm_mhz > peaks["sustained_mhz"]):
+        return "burst", peaks["bf16_burst"]
+    return "sustained", peaks["bf16"]
 
 
 # --------------------------------------------------------------------------
@@ -305,12 +328,20 @@ class FlashWorkload:
         self.forward()
         self.backward()
 
+    def units(self):
+        """(kv head, group) pairs: with K/V replicated over the group each is an
+        independent attention problem of `batch` slices."""
+        return self.q.shape[0]*self.q.shape[1]
+
+    def by_unit(self, t):
+        return t.view((t.shape[0]*t.shape[1],) + tuple(t.shape[2:]))
+
     def step_units(self, lo, hi):
-        """forward + backward of kv heads [lo, hi) only (views of the same buffers)."""
+        """forward + backward of units [lo, hi) only (views of the same buffers)."""
         ops = self.ops
         H, G, B = self.q.shape[:3]
-        nb = (hi - lo)*G*B
-        v = lambda t: t[lo:hi]
+        nb = (hi - lo)*B
+        v = lambda t: self.by_unit(t)[lo:hi]
         ops.fill(-math.inf, v(self.lse))
         ops.clear(v(self.y))
         ops.flash_sdpa_fwd(self.S, self.D, nb, v(self.k), v(self.q), self.mask, v(self.s_lse),
@@ -384,8 +415,13 @@ def run_gpu_arm(args):
         if rank == 0:
             print(json.dumps({"profile_run": True, "workload": args.workload, **res}), flush=True)
         return
-    cfg = C3 if args.workload == "c3" else C3_SMALL
-    wl = FlashWorkload(cfg, dev, seed=2 + rank)
+    from nntile_b200.parallel import shard_range
+    full_cfg = C3 if args.workload == "c3" else C3_SMALL
+    if full_cfg["kv_heads"] % world != 0:
+        raise SystemExit(f"{full_cfg['kv_heads']} kv heads do not divide over {world} ranks")
+    lo, hi = shard_range(full_cfg["kv_heads"], rank, world)
+    cfg = dict(full_cfg, kv_heads=hi - lo)       # this rank's block of (batch, kv head) units
+    wl = FlashWorkload(cfg, dev, seed=2 + 100*lo)
     fwd_path = ops.flash_sdpa_path(cfg["seq"], cfg["head"], wl.nb)
     bwd_path = ops.flash_sdpa_path(cfg["seq"], cfg["head"], wl.nb, backward=True)
 
@@ -413,24 +449,42 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     ms_per_step = total_ms/args.steps
-    flops_step = wl.flops_fwd + wl.flops_bwd
-    value = world*flops_step/(ms_per_step*1e-3)/1e12
+    flops_step = wl.flops_fwd + wl.flops_bwd          # this rank's shard
+    flops_job = sum(causal_flops(full_cfg))           # the whole problem
+    value = flops_job/(ms_per_step*1e-3)/1e12
 
     # ---- roofline of the dominant kernel (backward tile task) -----------------
     bwd_med = statistics.median(bwd_ms)
     fwd_med = statistics.median(fwd_ms)
     achieved = wl.flops_bwd/(bwd_med*1e-3)/1e12
+    regime, peak = roofline_regime(peaks, total_ms, clocks.get("sm_mhz"))
+    kernel_ms = bwd_med*NCU_BWD_KERNEL_SHARE
+    fwd_tf = wl.flops_fwd/(fwd_med*1e-3)/1e12
     roofline = {
         "bound": "tensor", "kernel": "flash_sdpa_bwd tile task",
-        "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
-        "frac": achieved/peaks["bf16"], "peak_source": peaks["source"] + " sustained bf16 GEMM",
+        "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved/peak,
+        "regime": regime,
+        "regime_rule": "burst peak if the timed region is under 1 s or the sampled median SM "
+                       "clock is above the clock the sustained peak was measured at",
+        "frac_burst": achieved/peaks["bf16_burst"], "frac_sustained": achieved/peaks["bf16"],
+        "peak_burst": peaks["bf16_burst"], "peak_sustained": peaks["bf16"],
+        "peak_source": peaks["source"] + " bf16 GEMM (" + regime + ")",
+        "timed_region_ms": total_ms,
+        "kernel_alone": {"name": "flash_bwd_kernel<128>", "ms": kernel_ms,
+                         "achieved": wl.flops_bwd/(kernel_ms*1e-3)/1e12,
+                         "frac": wl.flops_bwd/(kernel_ms*1e-3)/1e12/peak,
+                         "how": "tile-task time x the kernel's share of it in the ncu launch "
+                                "list (profiles/)", "share": NCU_BWD_KERNEL_SHARE},
+        "ms_x_mhz": (bwd_med*clocks["sm_mhz"] if clocks.get("sm_mhz") else None),
         "traffic": (NCU_DRAM_BYTES_PER_SLICE["flash_bwd_kernel<128>"]*wl.nb
                     if (cfg["head"], cfg["seq"]) == (128, 4096) and bwd_path == 2 else None),
         "traffic_note": "DRAM bytes per launch of flash_bwd_kernel<128> from a one-pass ncu capture "
                         "of the 128-slice workload, scaled by the slices of this launch (profiles/)",
-        "fwd": {"achieved": wl.flops_fwd/(fwd_med*1e-3)/1e12, "ms": fwd_med,
-                "frac": wl.flops_fwd/(fwd_med*1e-3)/1e12/peaks["bf16"]},
+        "fwd": {"achieved": fwd_tf, "ms": fwd_med, "frac": fwd_tf/peak,
+                "frac_burst": fwd_tf/peaks["bf16_burst"], "frac_sustained": fwd_tf/peaks["bf16"]},
         "bwd_ms": bwd_med,
+        "step": {"achieved": flops_step/(ms_per_step*1e-3)/1e12,
+                 "frac": flops_step/(ms_per_step*1e-3)/1e12/peak},
     }
 
     if args.profile:
@@ -449,10 +503,12 @@ def run_gpu_arm(args):
     dev_out = (wl.y, wl.dq, wl.dk, wl.dv)
 
     from nntile_b200.parallel import HostStream
-    pipe = HostStream(dev, cfg["kv_heads"], chunks=8)
+    pipe = HostStream(dev, wl.units(), chunks=8)
+    host_in, host_out = [wl.by_unit(x) for x in host_in], [wl.by_unit(x) for x in host_out]
+    dev_in, dev_out = [wl.by_unit(x) for x in dev_in], [wl.by_unit(x) for x in dev_out]
 
     def e2e_step():
-        # copies of one kv head overlap the kernels of the previous one
+        # copies of one chunk of units overlap the kernels of the previous one
         pipe.step(host_in, dev_in, wl.step_units, dev_out, host_out)
 
     e2e_ms, _, _ = time_steps(torch, e2e_step, e2e_steps, 1, barrier)
@@ -460,9 +516,10 @@ def run_gpu_arm(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())/e2e_steps
-    h2d = sum(x.numel()*x.element_size() for x in host_in)
-    d2h = sum(x.numel()*x.element_size() for x in host_out)
-    e2e = {"value": world*flops_step/(e2e_ms*1e-3)/1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+    # bytes of the whole job (every rank copies its shard)
+    h2d = world*sum(x.numel()*x.element_size() for x in host_in)
+    d2h = world*sum(x.numel()*x.element_size() for x in host_out)
+    e2e = {"value": flops_job/(e2e_ms*1e-3)/1e12, "unit": UNIT, "ms_per_step": e2e_ms,
            "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     del host_in, host_out
     if world == 1:
@@ -474,6 +531,10 @@ def run_gpu_arm(args):
             e2e["grouped_query_api"] = {"error": repr(ex)}
 
     extra, cpu_baseline = None, None
+    del wl
+    torch.cuda.empty_cache()
+    if world > 1:
+        extra = run_extras_multi(torch, dist, ops, dev, peaks, args, rank, world)
     if world == 1:
         extra = run_extras(torch, ops, lib, dev, peaks, args)
         backend, cores = cpu_arm_setup()
@@ -492,17 +553,20 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {
                 "workload": ("C3 llama-gqa attention fwd+bwd (BASELINE configs[2]): 32 q "
-                             "heads (8 kv x group 4), head_dim 128, seq 4096, batch 4 per GPU, "
-                             "causal, RoPE pre-applied, seq-tile 4096") if args.workload == "c3"
+                             "heads (8 kv x group 4), head_dim 128, seq 4096, batch 4, "
+                             "causal, RoPE pre-applied, seq-tile 4096; the 32 (batch, kv head) "
+                             "units dealt over the GPUs") if args.workload == "c3"
                             else "small profiling case of C3 (16 slices)",
-                "per_gpu_shape": cfg, "global_batch": cfg["batch"]*world,
+                "shape": full_cfg, "per_gpu_shape": cfg, "global_batch": full_cfg["batch"],
                 "flop_convention": "causal: fwd 2W, bwd 5W, W=B*Hq*S^2*D",
-                "l2": "inputs_exceed_l2 (Q,K,V,dY,A 134 MB each vs 126 MB L2)",
-                "parallelism": f"{world} independent shards of (batch, kv head) units, no collective",
+                "l2": ("inputs_exceed_l2 (Q,K,V,dY,A %d MB each per GPU vs 126 MB L2)"
+                       % (cfg["kv_heads"]*cfg["group"]*cfg["batch"]*cfg["seq"]*cfg["head"]*2 >> 20)),
+                "parallelism": f"{world} shards of {cfg['kv_heads']*cfg['batch']} (batch, kv head) "
+                               "units each, no collective",
                 "paths": {"fwd": fwd_path, "bwd": bwd_path,
                           "legend": "2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel"},
             },
@@ -514,29 +578,201 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-def run_extras(torch, ops, lib, dev, peaks, args):
-    """Configs 2, 4 and 5 at N=1 (few steps each)."""
+def run_extras_multi(torch, dist, ops, dev, peaks, args, rank, world):
+    """N > 1: config 5 with its batch split over the ranks (aggregate GB/s over the
+    slowest rank's time), and the weak-scaling line (every rank runs all of config 3)."""
+    from nntile_b200.parallel import shard_range
     out = {}
-    steps = max(3, min(args.steps, 10))
-    # ---- config 2: GPT-2-small attention, seq-tile 1024, head-tile 12, batch-tile 8
+    lo, hi = shard_range(C5["batch"], rank, world)
+    steps = max(12, min(args.steps*4, 40))
+    res = run_decode(torch, ops, dev, peaks, dict(C5, batch=hi - lo), steps, 5,
+                     barrier=dist.barrier)
+    t = torch.tensor([res["ms_per_step"]], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    nbytes = 2*C5["batch"]*C5["kv_heads"]*C5["max_seq"]*C5["head"]*2 \
+        + 2*C5["batch"]*C5["group"]*C5["kv_heads"]*C5["head"]*2
+    gbs = nbytes/(ms*1e-3)/1e9
+    out["c5_decode"] = {"gbs": gbs, "ms_per_step": ms, "bytes_per_step": nbytes,
+                        "frac_of_measured_hbm": gbs/(world*peaks["hbm"]),
+                        "peak_gbs": world*peaks["hbm"], "peak_source": peaks["source"],
+                        "shape": C5, "per_gpu_batch": hi - lo, "scaling": "strong",
+                        "note": "split-KV decode, batch split over the ranks, no collective; "
+                                "aggregate bytes over the slowest rank's time"}
+    wl = FlashWorkload(C3, dev, seed=2 + rank)
+    wsteps = max(3, min(args.steps, 10))
+    ms, _, _ = time_steps(torch, wl.step, wsteps, 3, dist.barrier)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())/wsteps
+    out["weak_scaling"] = {"tflops": world*(wl.flops_fwd + wl.flops_bwd)/(ms*1e-3)/1e12,
+                           "ms_per_step": ms, "global_batch": C3["batch"]*world,
+                           "note": "every rank runs all of config 3 on its own seed"}
+    del wl
+    return out
+
+
+def run_c2(torch, dev, steps):
+    """Config 2: GPT-2-small attention, seq-tile 1024, head-tile 12, batch-tile 8 - one
+    tile task per pass, 33 us of tensor work: launch-bound when every call comes from
+    Python, so the step is also captured once in a CUDA graph and replayed."""
     wl = FlashWorkload(C2, dev, seed=1, rope=False)
+    flops = wl.flops_fwd + wl.flops_bwd
     ms, _, _ = time_steps(torch, wl.step, steps*4, 3)
     ms /= steps*4
-    out["c2_gpt2_small_attention"] = {
-        "tflops": (wl.flops_fwd + wl.flops_bwd)/(ms*1e-3)/1e12, "ms_per_step": ms,
-        "shape": C2, "note": "one tile task per pass (batch tile 8, head tile 12); "
-                             "working set 63 MB fits L2"}
+    res = {"tflops": flops/(ms*1e-3)/1e12, "ms_per_step": ms, "shape": C2,
+           "note": "one tile task per pass (batch tile 8, head tile 12); working set 63 MB "
+                   "fits L2; calls issued one by one from Python"}
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                wl.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            wl.step()
+        reps = 200
+        gms, _, _ = time_steps(torch, graph.replay, reps, 5)
+        gms /= reps
+        res["cuda_graph"] = {"tflops": flops/(gms*1e-3)/1e12, "ms_per_step": gms, "replays": reps,
+                             "note": "the same step (8 launches) captured once, replayed"}
+    except Exception as exc:                     # informational; never breaks the line
+        res["cuda_graph"] = {"error": repr(exc)[:200]}
     del wl
+    return res
+
+
+def run_hbm_kernels(torch, ops, dev, peaks, steps):
+    """The HBM-bound kernels next to the fused pair, each timed alone on tensors far
+    larger than L2: the layout-change kernels around the SDPA layer at config 3's
+    shapes, and the unfused chain's kernels at config 1's per-head shapes scaled up to
+    2 GiB of logits.  GB/s = algorithmic bytes (one read + one write of the tensor,
+    plus the small operands) over the CUDA-event time."""
+    out = {}
+    hbm = peaks["hbm"]
+
+    def timed(fn, nbytes, reps=10):
+        ms, _, _ = time_steps(torch, fn, reps, 3)
+        ms /= reps
+        gbs = nbytes/(ms*1e-3)/1e9
+        return {"gbs": gbs, "ms": ms, "bytes": nbytes, "frac_of_measured_hbm": gbs/hbm}
+
+    g = torch.Generator(device=dev).manual_seed(5)
+    # ---- layout changes: config 3's Q (32 heads) and K (8 kv heads)
+    D, S, B = C3["head"], C3["seq"], C3["batch"]
+    for name, lead in (("q_32_heads", C3["group"]*C3["kv_heads"]), ("k_8_kv_heads", C3["kv_heads"])):
+        src = torch.randn((B, S, D, lead), generator=g, device=dev).to(torch.bfloat16)
+        dst = torch.empty((lead, B, S, D), dtype=torch.bfloat16, device=dev)
+        sc = torch.randn((B, S, D//2), generator=g, device=dev).to(torch.bfloat16)
+        nb = src.numel()*2
+        out[f"transpose_rope_{name}"] = timed(
+            lambda: ops.transpose_rope(lead, D, S, B, sc, sc, src, dst), 2*nb + 2*sc.numel()*2)
+        out[f"transpose_heads_back_{name}"] = timed(
+            lambda: ops.transpose_heads_back(lead, D, S, B, dst, src), 2*nb)
+        del src, dst, sc
+    # ---- unfused chain: logits [Sk, Sq, batch] in bf16 and fp32
+    Sk = Sq = 2048
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+        nbatch = 128 if dt == torch.bfloat16 else 64
+        es = 2 if dt == torch.bfloat16 else 4
+        logits = torch.randn((nbatch, Sq, Sk), generator=g, device=dev).to(dt)
+        nb = logits.numel()*es
+        mse = torch.zeros((nbatch, Sq, 2), dtype=dt, device=dev)
+        mask = torch.ones((Sq, Sk), dtype=torch.bool, device=dev).tril()
+        sl = torch.zeros((nbatch, Sq), dtype=dt, device=dev)
+        other = torch.randn((nbatch, Sq, Sk), generator=g, device=dev).to(dt)
+        out[f"mask_scalar_{tag}"] = timed(
+            lambda: ops.mask_scalar(Sk*Sq, nbatch, mask, -math.inf, logits), nb//2)
+        out[f"maxsumexp_{tag}"] = timed(
+            lambda: ops.maxsumexp(1, Sq*nbatch, Sk, logits, mse), nb)
+        out[f"softmax_inplace_{tag}"] = timed(
+            lambda: ops.softmax_inplace(1, Sq*nbatch, Sk, mse, 1.0, logits), 2*nb)
+        out[f"add_slice_inplace_{tag}"] = timed(
+            lambda: ops.add_slice_inplace(1, Sq*nbatch, Sk, -1.0, sl, 1.0, logits), 2*nb)
+        out[f"multiply_inplace_{tag}"] = timed(
+            lambda: ops.multiply_inplace(logits.numel(), 1.0, other, logits), 3*nb)
+        out[f"sumprod_slice_{tag}"] = timed(
+            lambda: ops.sumprod_slice(1, Sq*nbatch, Sk, 1.0, logits, other, 0.0, sl), 2*nb)
+        del logits, other, mse, sl
+    out["note"] = ("mask_scalar writes only the masked half (causal); bytes are algorithmic, "
+                   "peak = measured copy bandwidth")
+    return out
+
+
+def run_extras(torch, ops, lib, dev, peaks, args):
+    """Configs 2, 4 and 5 and the kernels beside the fused pair at N=1 (few steps each)."""
+    out = {}
+    steps = max(3, min(args.steps, 10))
+    out["c2_gpt2_small_attention"] = run_c2(torch, dev, steps)
     # ---- config 4: long context, seq-tile 2048, K/V tiles streamed through tasks
     out["c4_long_context"] = run_c4(torch, ops, lib, dev, steps)
     # ---- config 3 through the grouped-query entry points (K, V not replicated)
     out["c3_native_gqa"] = run_c3_gqa(torch, ops, dev, steps)
     # ---- config 5: decode, HBM-bound
     out["c5_decode"] = run_decode(torch, ops, dev, peaks, C5, steps*4, 5)
-    # ---- library comparator (context only, not the product): cuDNN's SDPA as the
-    # reference reaches it - additive bf16 bias, no causal flag - and with the flag
+    try:
+        out["hbm_bound_kernels"] = run_hbm_kernels(torch, ops, dev, peaks, steps)
+    except Exception as exc:                     # informational; never breaks the line
+        out["hbm_bound_kernels"] = {"error": repr(exc)[:200]}
+    torch.cuda.empty_cache()
+    # ---- comparators (context only, not the product): the reference's own GPU wrappers
+    # of the fused pair (cuDNN graph with the mask as bias + merge / add_inplace
+    # kernels), compiled in place as oracle/_ref_gpu; and cuDNN through torch
+    out["reference_gpu_wrappers_c3"] = run_reference_gpu(torch, dev)
     out["cudnn_comparator_c3"] = run_cudnn_comparator(torch, dev)
     return out
+
+
+def run_reference_gpu(torch, dev):
+    """Config 3's tile task through the reference's src/kernel/flash_sdpa_{fwd,bwd}_cudnn
+    wrappers (test infrastructure, never on the product path)."""
+    import ctypes
+    try:
+        import oracle as O
+        ref = O.ref_gpu()
+        if ref is None:
+            return {"unavailable": "oracle/_ref_gpu not built"}
+        S, D, nb = C3["seq"], C3["head"], C3["batch"]*C3["group"]*C3["kv_heads"]
+        g = torch.Generator(device=dev).manual_seed(9)
+        mk = lambda: torch.randn((nb, S, D), generator=g, device=dev).to(torch.bfloat16)
+        q, k, v, dy = mk(), mk(), mk(), mk()
+        mask = causal_mask_tile(S, "diag", dev)
+        lse = torch.empty((nb, S), dtype=torch.float32, device=dev)
+        A = torch.zeros_like(q)
+        s_l, s1, s2, s3 = torch.empty_like(lse), torch.empty_like(q), torch.empty_like(q), \
+            torch.empty_like(q)
+        dK, dQ, dV = (torch.zeros_like(q) for _ in range(3))
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        side = torch.cuda.Stream()          # the wrappers refuse the null stream
+        sp = ctypes.c_void_p(side.cuda_stream)
+        status = []
+
+        def step():
+            lse.fill_(-math.inf)
+            A.zero_()
+            status.append(ref.refgpu_flash_sdpa_fwd_bf16(sp, S, D, nb, p(k), p(q), p(mask), p(s_l),
+                                                         p(v), p(s1), p(lse), p(A)))
+            status.append(ref.refgpu_flash_sdpa_bwd_bf16(sp, S, D, nb, p(k), p(q), p(v), p(A), p(dy),
+                                                         p(mask), p(lse), p(s1), p(s2), p(s3),
+                                                         p(dK), p(dQ), p(dV)))
+
+        with torch.cuda.stream(side):
+            step()
+            side.synchronize()
+            if any(status):
+                return {"unavailable": f"reference wrapper status {status}"}
+            ms, _, _ = time_steps(torch, step, 5, 2)
+        ms /= 5
+        f, b = causal_flops(C3)
+        return {"ms_per_step": ms, "tflops": (f + b)/(ms*1e-3)/1e12,
+                "note": "the reference's own GPU path for one config-3 tile task (cuDNN bias-form "
+                        "graph into scratch, merge kernel, three add_inplace passes); "
+                        "causal-convention FLOPs although it executes all S^2"}
+    except Exception as exc:
+        return {"unavailable": repr(exc)[:200]}
 
 
 def run_e2e_gqa(torch, ops, dev, cfg, flops_step, steps):
@@ -638,7 +874,7 @@ def run_cudnn_comparator(torch, dev):
         return {"unavailable": repr(exc)[:200]}
 
 
-def run_decode(torch, ops, dev, peaks, c5, steps, warmup):
+def run_decode(torch, ops, dev, peaks, c5, steps, warmup, barrier=None):
     """One new token against the KV cache of config 5 (or a smaller batch of it)."""
     from nntile_b200.sdpa import decode_sdpa
     D, L, B, G, H = c5["head"], c5["max_seq"], c5["batch"], c5["group"], c5["kv_heads"]
@@ -649,7 +885,7 @@ def run_decode(torch, ops, dev, peaks, c5, steps, warmup):
     o = torch.empty_like(q)
     ws = torch.empty(ops.decode_workspace_bytes(D, L, B, G, H), dtype=torch.uint8, device=dev)
     fn = lambda: decode_sdpa(q, Kc, Vc, L, out=o, workspace=ws)
-    ms, _, _ = time_steps(torch, fn, steps, warmup)
+    ms, _, _ = time_steps(torch, fn, steps, warmup, barrier)
     ms /= steps
     nbytes = 2*B*H*L*D*2 + 2*B*G*H*D*2
     gbs = nbytes/(ms*1e-3)/1e9
@@ -691,7 +927,7 @@ def run_c4(torch, ops, lib, dev, steps):
     i64 = ctypes.c_int64
     shape = (i64*5)(D, S, 1, 1, H)
     base = (i64*5)(D, St, 1, 1, H)
-    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(base)
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(shape, base)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     pk = {n: parr(t) for n, t in dict(Q=Q, K=K, V=V, dY=dY, A=A, dQ=dQ, dK=dK, dV=dV, lse=lse,
                                       m=masks).items()}

@@ -126,6 +126,23 @@ int nntile_b200_accumulate_attn_output_bf16(nntile_b200_stream_t stream,
         int64_t head, int64_t seq, int64_t batch, const float *src_lse,
         const void *src_attn, float *dst_lse, void *dst_attn);
 
+/* Batched column-major GEMM, C[m,n,batch] = alpha*op(A)*op(B) + beta*C with packed
+ * leading dimensions and the matrices of a batch back to back; transA / transB are
+ * 0 (as stored) or 1 (transposed); alpha and beta act on the fp32 accumulator before
+ * the single rounding to the storage type.  `cublas_handle` is the caller's
+ * cublasHandle_t, already bound to the stream the work should run on - in the
+ * reference the StarPU worker's handle.  A library call in the reference and here
+ * (cublasGemmStridedBatchedEx, fp32 compute, looked up in the process at run time;
+ * NNTILE_B200_E_DEVICE if no cuBLAS can be found).
+ * Replaces nntile::kernel::cublas::gemm<T>, include/nntile/kernel/cublas.hh,
+ * src/kernel/cublas.cc:35-164 (same argument order). */
+int nntile_b200_gemm_fp32(void *cublas_handle, int transA, int transB, int64_t m,
+        int64_t n, int64_t k, int64_t batch, float alpha, const float *A, const float *B,
+        float beta, float *C);
+int nntile_b200_gemm_bf16(void *cublas_handle, int transA, int transB, int64_t m,
+        int64_t n, int64_t k, int64_t batch, float alpha, const void *A, const void *B,
+        float beta, void *C);
+
 /* ---------------------------------------------------------------------------
  * Fused flash SDPA, one (Q tile, K/V tile) task
  * ------------------------------------------------------------------------- */
@@ -138,6 +155,8 @@ int nntile_b200_accumulate_attn_output_bf16(nntile_b200_stream_t stream,
  * scratch_lse (seq*batch floats) and scratch_A (seq*head*batch bf16) are the two
  * scratch buffers the reference's tile layer hands to every task; they may be
  * overwritten with anything.  All pointers 16-byte aligned.
+ * For shapes the tcgen05 kernels take, the first 4 bytes of scratch_A are the task's
+ * status word (see nntile_b200_flash_sdpa_read_status).
  * Pointer order and semantics are those of
  * nntile::kernel::flash_sdpa_fwd_cudnn::execute_graph<bf16_t>,
  * include/nntile/kernel/flash_sdpa_fwd_cudnn/cuda.hh:37-76,
@@ -150,7 +169,8 @@ int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int64_t seq,
 
 /* Backward: dK, dQ, dV += gradients of one (Q tile, K/V tile) pair computed from
  * the GIVEN A (final output) and lse (final log-sum-exp) of the Q tile.
- * The three scratch buffers (each seq*head*batch bf16) may be overwritten.
+ * The three scratch buffers (each seq*head*batch bf16) may be overwritten; for shapes
+ * the tcgen05 kernels take, the first 4 bytes of scratch_dV are the task's status word.
  * Pointer order and semantics are those of
  * nntile::kernel::flash_sdpa_bwd_cudnn::execute_graph<bf16_t>,
  * include/nntile/kernel/flash_sdpa_bwd_cudnn/cuda.hh:29-59,
@@ -185,10 +205,71 @@ int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq
 size_t nntile_b200_flash_sdpa_gqa_scratch_bytes(int64_t seq, int64_t head,
         int64_t batch, int64_t group, int64_t kv_heads);
 
+/* Status word of the tcgen05 kernels.  Every wait inside them is bounded; a role
+ * that gives up (a copy or a product it waits for did not arrive within 200 ms)
+ * stores a code in a 32-bit word in device memory, the CTAs of the launch - and of
+ * every later launch that shares the word - skip their work, and the kernels return
+ * normally: the C call has long returned NNTILE_B200_OK by then, and the outputs of
+ * the skipped CTAs are NOT valid.  The word is the first 4 bytes of the buffer that
+ * carries the task's bookkeeping: scratch_A (forward tile task), scratch_dV (backward
+ * tile task), `scratch` (grouped-query and tensor-level entry points).  A tile-level
+ * call clears it when it starts; a tensor-level call clears it once and every one of
+ * its tasks shares it, so a give-up in any task stays visible (and stops the tasks
+ * behind it).  Codes: 0 clean; forward 1 producer, 2 MMA issuer, 3 softmax; backward
+ * 11 producer, 12 MMA issuer, 13 dQ drain, 14 softmax, 20 shared memory misaligned.
+ * This helper copies the word to the host: it SYNCHRONISES `stream` (the one call of
+ * this library that does) and is meant for after a step, not between tasks.
+ * No counterpart in the reference (cuDNN reports through its own status). */
+int nntile_b200_flash_sdpa_read_status(nntile_b200_stream_t stream, const void *scratch,
+        unsigned int *code);
+
+/* Test support, no counterpart in the reference: arms a one-shot hook for the NEXT
+ * tcgen05 forward launch of this process.  That launch runs a test instantiation of
+ * the kernel whose waits give up after 1 ms and whose producer withholds the first K
+ * copy, so that one wait runs out, the status word becomes non-zero and the kernel
+ * returns normally.  Nothing traps or spins; used by the test of the failure report. */
+void nntile_b200_test_arm_wait_timeout(void);
+
 /* Which implementation nntile_b200_flash_sdpa_{fwd,bwd}_bf16 pick for a shape:
  * 2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel, 0 = rejected. */
 int nntile_b200_flash_sdpa_fwd_path(int64_t seq, int64_t head, int64_t batch);
 int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_t batch);
+
+/* ---------------------------------------------------------------------------
+ * Layout changes around the SDPA layer, fused with their neighbours
+ * ------------------------------------------------------------------------- */
+
+/* dst[head, seq, batch, lead] = RoPE(src[lead, head, seq, batch]): the projection
+ * output (lead = group*kv_heads for Q, kv_heads for K, fastest index) brought into
+ * the SDPA layout and rotated in one pass.  sin, cos: bf16 [head/2, seq, batch] as
+ * the reference's attention layer fills them; both NULL = layout change only (V).
+ *   dst[2i, .., n]   = cos[i,..]*x[2i] - sin[i,..]*x[2i+1]
+ *   dst[2i+1, .., n] = sin[i,..]*x[2i] + cos[i,..]*x[2i+1],  x = src[n, :, ..]
+ * fp32 arithmetic without fused multiply-add, one rounding to bf16: bit-identical to
+ * the two reference passes.  lead and head even, pointers 16-byte aligned.
+ * Replaces transpose_async(1.0, src, tmp, ndim) followed by rope_async(sin, cos, tmp,
+ * dst) (wrappers/python/nntile/model/llama_attention.py:592-625; kernels
+ * nntile::kernel::transpose::cuda<T>, src/kernel/transpose/cuda.cu:24-132, and
+ * nntile::kernel::rope::cuda<T>, src/kernel/rope/cuda.cu:21-57).  Together with the
+ * grouped-query entry points below the K/V replication (add_slice_inplace, :605-616)
+ * disappears as well. */
+int nntile_b200_transpose_rope_bf16(nntile_b200_stream_t stream, int64_t lead,
+        int64_t head, int64_t seq, int64_t batch, const void *sin, const void *cos,
+        const void *src, void *dst);
+
+/* dst[head, seq, batch, lead] = src[lead, head, seq, batch] + bias[head, lead]:
+ * GPT-2's prologue, transpose_async + add_fiber_inplace_async(1.0, bias, 1.0, dst, 0, 1)
+ * (wrappers/python/nntile/model/gpt2_attention.py:258-273; kernel
+ * src/kernel/add_fiber_inplace/cuda.cu) in one pass, one rounding. */
+int nntile_b200_transpose_bias_bf16(nntile_b200_stream_t stream, int64_t lead,
+        int64_t head, int64_t seq, int64_t batch, const void *bias, const void *src,
+        void *dst);
+
+/* dst[lead, head, seq, batch] = src[head, seq, batch, lead]: the attention output
+ * brought back for the output projection (transpose_async(1.0, A, At, 3),
+ * llama_attention.py:620-623, gpt2_attention.py:270-272). */
+int nntile_b200_transpose_heads_back_bf16(nntile_b200_stream_t stream, int64_t lead,
+        int64_t head, int64_t seq, int64_t batch, const void *src, void *dst);
 
 /* ---------------------------------------------------------------------------
  * Decode: one new query token against a KV cache, split over the cache length
@@ -263,9 +344,19 @@ size_t nntile_b200_decode_sdpa_noalloc_max_bytes(void);
  * its (K/V tile, Q tile) pair as fully masked and no task is generated for it
  * (under a causal mask 44 % of the pairs of config 4), and several entries may point
  * to the same buffer, so a causal mask needs one zero tile and one diagonal tile
- * instead of a dense [seq, seq] tensor.  The caller runs the prologue (lse = -inf, A = 0) for the forward
- * and provides `scratch` of nntile_b200_tensor_flash_sdpa_scratch_bytes(basetile)
- * bytes, 256-byte aligned, reused by every task.
+ * instead of a dense [seq, seq] tensor.  The caller runs the prologue (lse = -inf,
+ * A = 0) for the forward and provides `scratch` of
+ * nntile_b200_tensor_flash_sdpa_scratch_bytes(shape, basetile) bytes, 256-byte
+ * aligned (status word, mask class tables, and for the backward delta, lse*log2e and
+ * an fp32 dQ accumulator for the whole tensor).
+ * Scheduling: the reference gives every pair to StarPU, which overlaps tasks of
+ * different output tiles.  Here the caller's stream forks into a per-device pool of
+ * helper streams (created on the first call on a device) and joins again before the
+ * call returns, so all work is ordered after what precedes the call on `stream` and
+ * before what follows it.  Tasks that merge into the same (lse, A) run in K/V-tile
+ * order; tasks that add into the same dK/dV tile run in Q-tile order; dQ of a Q tile
+ * is summed in fp32 over all its K/V tiles and rounded into dQ once (the reference
+ * rounds per task).  Every distinct mask buffer is classified once per call.
  * Replace nntile::tensor::flash_sdpa_fwd_cudnn_async<bf16_t>,
  * src/tensor/flash_sdpa_fwd_cudnn.cc:211-279 (+ src/tile/flash_sdpa_fwd_cudnn.cc:161-196)
  * and nntile::tensor::flash_sdpa_bwd_cudnn_async<bf16_t>,
@@ -282,7 +373,27 @@ int nntile_b200_tensor_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream,
         const void *const *mask_tiles, const float *const *lse_tiles,
         void *const *dK_tiles, void *const *dQ_tiles, void *const *dV_tiles,
         void *scratch, size_t scratch_bytes);
-size_t nntile_b200_tensor_flash_sdpa_scratch_bytes(const int64_t *basetile);
+size_t nntile_b200_tensor_flash_sdpa_scratch_bytes(const int64_t *shape,
+        const int64_t *basetile);
+
+/* Grouped-query form of the tensor-level loops: Q, A, dA, dQ, lse tiled as above,
+ * K, V, dK, dV are [head, seq, batch, kv_heads] tensors tiled
+ * [head, basetile[1], basetile[2], basetile[4]] (tile (s, b, h) at
+ * s + nseq*(b + nbatch*h)), not replicated over the group - what the reference's
+ * attention layers hold before add_slice_inplace replicates them
+ * (wrappers/python/nntile/model/llama_attention.py:605-616).  tcgen05 shapes only. */
+int nntile_b200_tensor_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *mask_tiles,
+        float *const *lse_tiles, const void *const *V_tiles, void *const *A_tiles,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_tensor_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *V_tiles,
+        const void *const *A_tiles, const void *const *dA_tiles,
+        const void *const *mask_tiles, const float *const *lse_tiles,
+        void *const *dK_tiles, void *const *dQ_tiles, void *const *dV_tiles,
+        void *scratch, size_t scratch_bytes);
 
 #ifdef __cplusplus
 }

@@ -14,7 +14,8 @@
 //   add_slice_inplace,multiply_inplace,add_inplace,accumulate_attn_output}/cuda.hh:25,
 //   include/nntile/kernel/flash_sdpa_fwd_cudnn/cuda.hh:37-76 and
 //   include/nntile/kernel/flash_sdpa_bwd_cudnn/cuda.hh:29-59 (execute_graph without
-//   the cudnnHandle_t / graph pair).
+//   the cudnnHandle_t / graph pair),
+//   include/nntile/kernel/cublas.hh (cublas::gemm<T>, src/kernel/cublas.cc:35-164).
 #pragma once
 
 #include <cstdint>
@@ -30,8 +31,15 @@ using Scalar = float;
 struct fp32_t { float value; };
 struct bf16_t { std::uint16_t value; };
 struct bool_t { bool value; };
+// transposition flag of the reference's GEMM wrappers (include/nntile/constants.hh)
+struct TransOp
+{
+    enum Value : int { NoTrans, Trans } value;
+    constexpr explicit TransOp(Value v): value(v) {}
+};
 } // namespace nntile
 typedef struct CUstream_st *cudaStream_t;
+typedef struct cublasContext *cublasHandle_t;
 #endif
 
 namespace nntile_b200
@@ -156,6 +164,22 @@ void cuda(cudaStream_t stream, Index head, Index seq, Index batch, const fp32_t 
             reinterpret_cast<float *>(dst_lse), reinterpret_cast<P *>(dst_attn));
 }
 } // namespace accumulate_attn_output
+
+// The library GEMM of the unfused chain, with the reference's argument order; the
+// handle is the calling worker's cublasHandle_t, already bound to its stream.
+namespace cublas
+{
+template<typename T>
+void gemm(cublasHandle_t handle, TransOp transA, TransOp transB, Index m, Index n, Index k,
+        Index batch, Scalar alpha, const T *A, const T *B, Scalar beta, T *C) noexcept
+{
+    using P = std::conditional_t<nntile_b200::is_fp32<T>, float, void>;
+    NNTILE_B200_DISPATCH(T, gemm, handle, transA.value == TransOp::Trans ? 1 : 0,
+            transB.value == TransOp::Trans ? 1 : 0, m, n, k, batch, alpha,
+            reinterpret_cast<const P *>(A), reinterpret_cast<const P *>(B), beta,
+            reinterpret_cast<P *>(C));
+}
+} // namespace cublas
 
 // The fused pair: pointer order of the reference's execute_graph, stream instead of
 // the cuDNN handle and graph.  bf16 only (fp32 is rejected by the reference too).

@@ -5,9 +5,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# NNTILE_B200_LIB points at an alternative build of the same library (e.g. one
-# compiled with instrumentation); the default is the in-tree build.
-LIB_PATH = os.environ.get("NNTILE_B200_LIB") or os.path.join(_HERE, "csrc", "libnntile_b200.so")
+LIB_PATH = os.path.join(_HERE, "csrc", "libnntile_b200.so")
 
 i64, f32, vp, sz = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 _pp = ctypes.POINTER(ctypes.c_void_p)
@@ -45,7 +43,18 @@ SIGNATURES = {
     "nntile_b200_decode_sdpa_noalloc_max_bytes": ([], sz),
     "nntile_b200_tensor_flash_sdpa_fwd_bf16": ([vp, _pi, _pi] + [_pp]*6 + [vp, sz], ctypes.c_int),
     "nntile_b200_tensor_flash_sdpa_bwd_bf16": ([vp, _pi, _pi] + [_pp]*10 + [vp, sz], ctypes.c_int),
-    "nntile_b200_tensor_flash_sdpa_scratch_bytes": ([_pi], sz),
+    "nntile_b200_tensor_flash_sdpa_scratch_bytes": ([_pi, _pi], sz),
+    "nntile_b200_tensor_flash_sdpa_fwd_gqa_bf16": ([vp, _pi, _pi] + [_pp]*6 + [vp, sz], ctypes.c_int),
+    "nntile_b200_tensor_flash_sdpa_bwd_gqa_bf16": ([vp, _pi, _pi] + [_pp]*10 + [vp, sz], ctypes.c_int),
+    "nntile_b200_gemm_fp32": ([vp, ctypes.c_int, ctypes.c_int] + [i64]*4 + [f32, vp, vp, f32, vp],
+                              ctypes.c_int),
+    "nntile_b200_gemm_bf16": ([vp, ctypes.c_int, ctypes.c_int] + [i64]*4 + [f32, vp, vp, f32, vp],
+                              ctypes.c_int),
+    "nntile_b200_flash_sdpa_read_status": ([vp, vp, ctypes.POINTER(ctypes.c_uint)], ctypes.c_int),
+    "nntile_b200_test_arm_wait_timeout": ([], None),
+    "nntile_b200_transpose_rope_bf16": ([vp] + [i64]*4 + [vp]*4, ctypes.c_int),
+    "nntile_b200_transpose_bias_bf16": ([vp] + [i64]*4 + [vp]*3, ctypes.c_int),
+    "nntile_b200_transpose_heads_back_bf16": ([vp] + [i64]*4 + [vp]*2, ctypes.c_int),
 }
 for _name, _args in _TYPED.items():
     for _sfx in ("fp32", "bf16"):

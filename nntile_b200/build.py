@@ -4,8 +4,9 @@
 
 One nvcc invocation per source (object files are cached under csrc/build/), then
 one link step into ``csrc/libnntile_b200.so``.  nvcc cross-compiles without a
-GPU.  The library has no dependency beyond the CUDA runtime (linked statically)
-- the driver entry point needed for TMA descriptors is looked up at run time.
+GPU.  The library has no link-time dependency beyond the CUDA runtime (linked
+statically): the driver entry point needed for TMA descriptors and the cuBLAS
+routine behind the GEMM entry points are looked up at run time.
 """
 from __future__ import annotations
 
@@ -21,7 +22,8 @@ OBJ_DIR = os.path.join(CSRC, "build")
 LIB = os.path.join(CSRC, "libnntile_b200.so")
 SOURCES = [
     "vanilla_ops.cu", "flash_generic.cu", "flash_api.cu", "decode.cu",
-    "flash_fwd_sm100.cu", "flash_bwd_sm100.cu", "host_tensor.cu",
+    "flash_fwd_sm100.cu", "flash_bwd_sm100.cu", "host_tensor.cu", "gemm_cublas.cu",
+    "sdpa_prologue.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -36,7 +38,7 @@ def _nvcc() -> str:
 
 def _deps(src: str) -> list[str]:
     deps = [os.path.join(CSRC, src)]
-    deps += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    deps += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".hh"))]
     deps.append(os.path.join(os.path.dirname(HERE), "include", "nntile_b200.h"))
     return deps
 
@@ -68,7 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs = list(ex.map(lambda s: _compile(s, force), srcs))
     if force or _stale(LIB, objs):
         cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode",
-               "arch=compute_100a,code=sm_100a"]
+               "arch=compute_100a,code=sm_100a", "-ldl"]
         subprocess.run(cmd, check=True)
     if verbose:
         for o in objs:

@@ -16,18 +16,85 @@ int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const bf16 *A, const
 
 // tcgen05 / TMEM / TMA kernels (flash_fwd_sm100.cu, flash_bwd_sm100.cu):
 // head in {64, 128}, seq a multiple of 128.
+//
+// Bookkeeping of a tile task in device memory.  `status` is the 32-bit status
+// word (0 = every bounded wait completed; see STATUS_* below), `cls` the class
+// table [query block][key block] of the task's mask tile.  A tile-level call
+// carves both out of the scratch buffer of the task (status at offset 0, table
+// at CLS_OFFSET), classifies the mask and clears the word itself; the
+// tensor-level loops classify every distinct mask buffer once per call, keep one
+// status word for the whole call that no task clears, and pass `classify = false`.
+struct FwdAux
+{
+    uint32_t *status;
+    uint8_t *cls;
+    bool classify;
+};
+
+// Backward bookkeeping: besides the two above, delta = -rowsum(A o dA) and
+// lse2 = -lse*log2(e) (rows floats each) and the fp32 dQ accumulator, split at
+// `half_rows` over two buffers.  `phases` selects what a call enqueues, so that
+// the tensor-level loops can prepare and finish a Q tile once for all its K/V
+// tiles instead of once per pair.
+enum : int
+{
+    BWD_CLASSIFY = 1,   // classify the mask into `cls`, clear `status`
+    BWD_PREP = 2,       // delta, lse2, clear the accumulator
+    BWD_MAIN = 4,       // the tcgen05 kernel: dK, dV += ..., accumulator += dQ
+    BWD_FINISH = 8,     // dQ += bf16(scale * accumulator)
+    BWD_ALL = 15
+};
+
+struct BwdAux
+{
+    uint32_t *status;
+    uint8_t *cls;
+    float *delta, *lse2;
+    float *acc_lo, *acc_hi;
+    Index half_rows;
+    int phases;
+};
+
 bool flash_fwd_sm100_supports(Index seq, Index head, Index batch);
 // K, V (and dK, dV) may be shared by `kv_group` consecutive groups of `kv_batch`
 // batch entries: entry b uses K/V entry (b % kv_batch) + kv_batch*(b/(kv_batch*kv_group)).
 // kv_group = 1, kv_batch = batch is the plain one-to-one case.
 int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A,
-        void *scratch, size_t scratch_bytes, Index kv_group, Index kv_batch);
+        const FwdAux &aux, Index kv_group, Index kv_batch);
 bool flash_bwd_sm100_supports(Index seq, Index head, Index batch);
 int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
-        const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV,
-        bf16 *dK, bf16 *dQ, bf16 *dV, Index kv_group, Index kv_batch);
+        const float *lse, const BwdAux &aux, bf16 *dK, bf16 *dQ, bf16 *dV, Index kv_group,
+        Index kv_batch);
+// Layout the tile-level entry points give the three scratch buffers of a backward
+// task (status + class table + delta + lse2 in scratch_dV, the accumulator halves
+// in scratch_dQ and scratch_dK).
+BwdAux bwd_aux_from_scratch(Index seq, Index batch, void *scratch_dK, void *scratch_dQ,
+        void *scratch_dV);
+// Bytes of scratch_dV the layout above needs.
+size_t bwd_aux_bytes(Index seq, Index batch);
+
+// Entry points shared by the C wrappers (flash_api.cu) and the tensor-level
+// loops (host_tensor.cu): argument checks and the choice between the tcgen05
+// and the generic kernels.  `fwd_aux` / `bwd_aux` may be null: the bookkeeping
+// is then carved out of the scratch buffers as the tile-level C ABI documents.
+int flash_fwd_task(cudaStream_t s, Index seq, Index head, Index batch, const void *K,
+        const void *Q, const void *mask, const void *V, void *scratch_A, float *lse, void *A,
+        const FwdAux *fwd_aux);
+int flash_bwd_task(cudaStream_t s, Index seq, Index head, Index batch, const void *K,
+        const void *Q, const void *V, const void *A, const void *dA, const void *mask,
+        const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK,
+        void *dQ, void *dV, const BwdAux *bwd_aux);
+
+// Values of the status word: which role of which kernel gave up first.
+enum : uint32_t
+{
+    STATUS_OK = 0,
+    STATUS_FWD_PRODUCER = 1, STATUS_FWD_MMA = 2, STATUS_FWD_SOFTMAX = 3,
+    STATUS_BWD_PRODUCER = 11, STATUS_BWD_MMA = 12, STATUS_BWD_DRAIN = 13,
+    STATUS_BWD_SOFTMAX = 14, STATUS_BWD_SMEM_ALIGN = 20
+};
 
 // Classes of a 128x128 block of the additive mask [seq_q][seq_k].
 enum : uint8_t
@@ -54,11 +121,7 @@ constexpr size_t L2_GROUP_BYTES = (size_t)64 << 20;
 
 inline int l2_group_size(Index batch, size_t bytes_per_entry)
 {
-    size_t budget = L2_GROUP_BYTES;
-#ifdef NB200_EXP_ENV
-    if(const char *e = getenv("NB200_L2_GROUP_MB")) budget = (size_t)atoi(e) << 20;
-#endif
-    const size_t g = budget/(bytes_per_entry > 0 ? bytes_per_entry : 1);
+    const size_t g = L2_GROUP_BYTES/(bytes_per_entry > 0 ? bytes_per_entry : 1);
     return (int)(g < 1 ? 1 : (g > (size_t)batch ? (size_t)batch : g));
 }
 
@@ -73,8 +136,9 @@ __device__ __forceinline__ void group_decode(unsigned cta, int nunits, int batch
     b = (int)g*gsz + (int)(rem - (unsigned)unit*cur);
 }
 
-// Classify every block of `mask` into scratch + CLS_OFFSET and clear the status
-// word (flash_fwd_sm100.cu).
-int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *scratch);
+// Classify every block of `mask` into `cls` and, when `status` is not null, clear
+// that status word (flash_fwd_sm100.cu).
+int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *cls,
+        uint32_t *status);
 
 } // namespace nb200

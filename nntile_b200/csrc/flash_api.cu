@@ -24,51 +24,73 @@ extern "C" int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_
     return flash_bwd_sm100_supports(seq, head, batch) ? 2 : 1;
 }
 
-extern "C" int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int64_t seq,
-        int64_t head, int64_t batch, const void *K, const void *Q, const void *mask,
-        float *scratch_lse, const void *V, void *scratch_A, float *lse, void *A)
+namespace nb200 {
+
+int flash_fwd_task(cudaStream_t stream, Index seq, Index head, Index batch, const void *K,
+        const void *Q, const void *mask, const void *V, void *scratch_A, float *lse, void *A,
+        const FwdAux *fwd_aux)
 {
     int st = check_common(seq, head, batch);
     if(st != NNTILE_B200_OK) return st;
     if(seq == 0 || head == 0 || batch == 0) return NNTILE_B200_OK;
     if(!K || !Q || !mask || !V || !lse || !A) return NNTILE_B200_E_BADARG;
-    (void)scratch_lse;
     if(flash_fwd_sm100_supports(seq, head, batch))
     {
-        if(!scratch_A) return NNTILE_B200_E_BADARG;
+        if(!fwd_aux && !scratch_A) return NNTILE_B200_E_BADARG;
         if(!aligned16(K) || !aligned16(Q) || !aligned16(V) || !aligned16(A)
-                || !aligned16(mask) || !aligned16(scratch_A))
+                || !aligned16(mask) || (!fwd_aux && !aligned16(scratch_A)))
         {
             return NNTILE_B200_E_ALIGN;
         }
-        return flash_fwd_sm100(as_stream(stream), seq, head, batch, (const bf16 *)K,
-                (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A,
-                scratch_A, (size_t)seq*head*batch*sizeof(bf16), 1, batch);
+        FwdAux aux;
+        if(fwd_aux)
+        {
+            aux = *fwd_aux;
+        }
+        else
+        {
+            // status word + class table at the start of the task's scratch buffer
+            const size_t nblk = (size_t)(seq/128);
+            if((size_t)seq*head*batch*sizeof(bf16) < CLS_OFFSET + nblk*nblk)
+            {
+                return NNTILE_B200_E_SCRATCH;
+            }
+            uint8_t *sc = static_cast<uint8_t *>(scratch_A);
+            aux.status = reinterpret_cast<uint32_t *>(sc);
+            aux.cls = sc + CLS_OFFSET;
+            aux.classify = true;
+        }
+        return flash_fwd_sm100(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
+                (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A, aux, 1, batch);
     }
-    return flash_fwd_generic(as_stream(stream), seq, head, batch, (const bf16 *)K,
-            (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A);
+    return flash_fwd_generic(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
+            (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A);
 }
 
-extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int64_t seq,
-        int64_t head, int64_t batch, const void *K, const void *Q, const void *V,
-        const void *A, const void *dA, const void *mask, const float *lse,
-        void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ, void *dV)
+int flash_bwd_task(cudaStream_t stream, Index seq, Index head, Index batch, const void *K,
+        const void *Q, const void *V, const void *A, const void *dA, const void *mask,
+        const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK,
+        void *dQ, void *dV, const BwdAux *bwd_aux)
 {
     int st = check_common(seq, head, batch);
     if(st != NNTILE_B200_OK) return st;
     if(seq == 0 || head == 0 || batch == 0) return NNTILE_B200_OK;
-    if(!K || !Q || !V || !A || !dA || !mask || !lse || !dK || !dQ || !dV
-            || !scratch_dK || !scratch_dQ || !scratch_dV)
+    if(!K || !Q || !V || !A || !dA || !mask || !lse || !dK || !dQ || !dV)
     {
         return NNTILE_B200_E_BADARG;
     }
-    // delta (seq*batch floats) lives in scratch_dV: needs head >= 2
-    if(head < 2) return NNTILE_B200_E_SHAPE;
-    if(!aligned16(scratch_dV) || !aligned16(scratch_dQ) || !aligned16(scratch_dK))
+    const bool fast = flash_bwd_sm100_supports(seq, head, batch);
+    if(!(bwd_aux && fast))
     {
-        return NNTILE_B200_E_ALIGN;
+        if(!scratch_dK || !scratch_dQ || !scratch_dV) return NNTILE_B200_E_BADARG;
+        // delta (seq*batch floats) lives in scratch_dV: needs head >= 2
+        if(head < 2) return NNTILE_B200_E_SHAPE;
+        if(!aligned16(scratch_dV) || !aligned16(scratch_dQ) || !aligned16(scratch_dK))
+        {
+            return NNTILE_B200_E_ALIGN;
+        }
     }
-    if(flash_bwd_sm100_supports(seq, head, batch))
+    if(fast)
     {
         if(!aligned16(K) || !aligned16(Q) || !aligned16(V) || !aligned16(A)
                 || !aligned16(dA) || !aligned16(mask) || !aligned16(dK)
@@ -76,15 +98,52 @@ extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int6
         {
             return NNTILE_B200_E_ALIGN;
         }
-        return flash_bwd_sm100(as_stream(stream), seq, head, batch, (const bf16 *)K,
-                (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
-                (const bf16 *)mask, lse, scratch_dK, scratch_dQ, scratch_dV,
+        const BwdAux aux = bwd_aux ? *bwd_aux
+                : bwd_aux_from_scratch(seq, batch, scratch_dK, scratch_dQ, scratch_dV);
+        return flash_bwd_sm100(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
+                (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA, (const bf16 *)mask, lse, aux,
                 (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV, 1, batch);
     }
-    return flash_bwd_generic(as_stream(stream), seq, head, batch, (const bf16 *)K,
-            (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
-            (const bf16 *)mask, lse, (float *)scratch_dV, (bf16 *)dK, (bf16 *)dQ,
-            (bf16 *)dV);
+    return flash_bwd_generic(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
+            (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA, (const bf16 *)mask, lse,
+            (float *)scratch_dV, (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV);
+}
+
+} // namespace nb200
+
+extern "C" int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q, const void *mask,
+        float *scratch_lse, const void *V, void *scratch_A, float *lse, void *A)
+{
+    (void)scratch_lse;
+    return flash_fwd_task(as_stream(stream), seq, head, batch, K, Q, mask, V, scratch_A, lse, A,
+            nullptr);
+}
+
+extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q, const void *V,
+        const void *A, const void *dA, const void *mask, const float *lse,
+        void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ, void *dV)
+{
+    return flash_bwd_task(as_stream(stream), seq, head, batch, K, Q, V, A, dA, mask, lse,
+            scratch_dK, scratch_dQ, scratch_dV, dK, dQ, dV, nullptr);
+}
+
+// The status word of the fused kernels sits in the first four bytes of the scratch
+// buffer that carries a task's bookkeeping; this reads it back after the stream
+// has drained.
+extern "C" int nntile_b200_flash_sdpa_read_status(nntile_b200_stream_t stream,
+        const void *scratch, unsigned int *code)
+{
+    if(!scratch || !code) return NNTILE_B200_E_BADARG;
+    uint32_t word = 0;
+    if(cudaMemcpyAsync(&word, scratch, sizeof(word), cudaMemcpyDeviceToHost, as_stream(stream))
+            != cudaSuccess || cudaStreamSynchronize(as_stream(stream)) != cudaSuccess)
+    {
+        return NNTILE_B200_E_LAUNCH;
+    }
+    *code = word;
+    return NNTILE_B200_OK;
 }
 
 // ------------------------------------------------------------ grouped-query form
@@ -121,9 +180,13 @@ extern "C" int nntile_b200_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream, 
     {
         return NNTILE_B200_E_ALIGN;
     }
+    const size_t nblk = (size_t)(seq/128);
+    if(scratch_bytes < CLS_OFFSET + nblk*nblk) return NNTILE_B200_E_SCRATCH;
+    uint8_t *sc = static_cast<uint8_t *>(scratch);
+    const FwdAux aux = {reinterpret_cast<uint32_t *>(sc), sc + CLS_OFFSET, true};
     return flash_fwd_sm100(as_stream(stream), seq, head, slices, (const bf16 *)K,
-            (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A, scratch,
-            scratch_bytes, group, batch);
+            (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A, aux, group,
+            batch);
 }
 
 extern "C" int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
@@ -152,8 +215,8 @@ extern "C" int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, 
     }
     const size_t part = (size_t)seq*head*slices*2;        // one bf16 tensor of Q's shape
     uint8_t *sc = static_cast<uint8_t *>(scratch);
+    const BwdAux aux = bwd_aux_from_scratch(seq, slices, sc + 2*part, sc + part, sc);
     return flash_bwd_sm100(as_stream(stream), seq, head, slices, (const bf16 *)K,
             (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
-            (const bf16 *)mask, lse, sc + 2*part, sc + part, sc, (bf16 *)dK, (bf16 *)dQ,
-            (bf16 *)dV, group, batch);
+            (const bf16 *)mask, lse, aux, (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV, group, batch);
 }

@@ -47,6 +47,7 @@
 // hands to every task (they only ever held cuDNN's scratch gradients), so the
 // library allocates nothing.  All waits are bounded (sm100.cuh).
 #include "flash.cuh"
+#include "per_device.hh"
 #include "sm100.cuh"
 
 namespace nb200 {
@@ -73,13 +74,7 @@ __device__ unsigned long long g_prof[32];
 
 constexpr int BLK = 128;
 constexpr int THREADS = 512;
-#ifndef NB200_RED_PACE
-#define NB200_RED_PACE 24
-#endif
-#ifndef NB200_RED_BURST
-#define NB200_RED_BURST 4
-#endif
-constexpr int RED_PACE = NB200_RED_PACE, RED_BURST = NB200_RED_BURST;
+constexpr int RED_PACE = 24, RED_BURST = 4;   // dQ drain: 4 reductions, then wait for the schedule
 constexpr int MAX_BLOCKS = 256;      // seq <= 32768
 constexpr float LOG2E_F = 1.4426950408889634f;
 
@@ -293,7 +288,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     {
         if(threadIdx.x == 0)
         {
-            atomicExch(status, 20u);
+            atomicCAS(status, 0u, STATUS_BWD_SMEM_ALIGN);
         }
         return;
     }
@@ -429,7 +424,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
             if(!ok)
             {
-                atomicExch(status, 11u);
+                atomicCAS(status, 0u, STATUS_BWD_PRODUCER);
             }
         }
     }
@@ -596,7 +591,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
             if(!ok)
             {
-                atomicExch(status, 12u);
+                atomicCAS(status, 0u, STATUS_BWD_MMA);
             }
         }
     }
@@ -691,7 +686,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
         if(!ok && lane == 0)
         {
-            atomicExch(status, 13u);
+            atomicCAS(status, 0u, STATUS_BWD_DRAIN);
         }
     }
     else
@@ -916,7 +911,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
         if(!ok && lane == 0)
         {
-            atomicExch(status, 14u);
+            atomicCAS(status, 0u, STATUS_BWD_SOFTMAX);
         }
 #ifdef NB200_PROF
         if(ts == 0)
@@ -978,6 +973,12 @@ extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out32, int reset)
 }
 #endif
 
+size_t bwd_aux_bytes(Index seq, Index batch)
+{
+    const Index rows = batch*seq, nblk = seq/bwd::BLK;
+    return (size_t)(((CLS_OFFSET + nblk*nblk + 255) & ~(Index)255) + 8*rows);
+}
+
 bool flash_bwd_sm100_supports(Index seq, Index head, Index batch)
 {
     if(!((head == 64 || head == 128) && seq >= bwd::BLK && seq % bwd::BLK == 0
@@ -986,84 +987,115 @@ bool flash_bwd_sm100_supports(Index seq, Index head, Index batch)
         return false;
     }
     // scratch_dV must hold status + class table + delta + lse2
+    return bwd_aux_bytes(seq, batch) <= (size_t)(batch*seq*head*2);
+}
+
+BwdAux bwd_aux_from_scratch(Index seq, Index batch, void *scratch_dK, void *scratch_dQ,
+        void *scratch_dV)
+{
     const Index rows = batch*seq, nblk = seq/bwd::BLK;
-    const Index need = ((CLS_OFFSET + nblk*nblk + 255) & ~(Index)255) + 8*rows;
-    return need <= rows*head*2;
+    uint8_t *sc = static_cast<uint8_t *>(scratch_dV);
+    const size_t stats_off = (CLS_OFFSET + (size_t)nblk*nblk + 255) & ~(size_t)255;
+    BwdAux aux;
+    aux.status = reinterpret_cast<uint32_t *>(sc);
+    aux.cls = sc + CLS_OFFSET;
+    aux.delta = reinterpret_cast<float *>(sc + stats_off);
+    aux.lse2 = aux.delta + rows;
+    aux.acc_lo = static_cast<float *>(scratch_dQ);
+    aux.acc_hi = static_cast<float *>(scratch_dK);
+    aux.half_rows = rows/2;
+    aux.phases = BWD_ALL;
+    return aux;
 }
 
 template<int D>
 static int bwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index kv_batch,
         const bf16 *K, const bf16 *Q,
         const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask, const float *lse,
-        void *scratch_dK, void *scratch_dQ, void *scratch_dV, bf16 *dK, bf16 *dQ, bf16 *dV)
+        const BwdAux &aux, bf16 *dK, bf16 *dQ, bf16 *dV)
 {
     using namespace bwd;
     const Index rows = batch*seq;
     const int nblk = (int)(seq/BLK);
-    uint8_t *sc = static_cast<uint8_t *>(scratch_dV);
-    const size_t stats_off = (CLS_OFFSET + (size_t)nblk*nblk + 255) & ~(size_t)255;
-    float *delta = reinterpret_cast<float *>(sc + stats_off);
-    float *lse2 = delta + rows;
-    float *acc_lo = static_cast<float *>(scratch_dQ), *acc_hi = static_cast<float *>(scratch_dK);
-    const Index half_rows = rows/2;
-    int st = launch_mask_classify(s, (int)seq, mask, sc);
-    if(st != NNTILE_B200_OK)
-    {
-        return st;
-    }
-    bwd_prep_kernel<<<(unsigned)((rows*(D/8) + 255)/256), 256, 0, s>>>(D, rows, half_rows, A, dA,
-            lse, delta, lse2, acc_lo, acc_hi);
-    if(launch_status() != NNTILE_B200_OK)
-    {
-        return NNTILE_B200_E_LAUNCH;
-    }
-    CUtensorMap tk, tv, tq, tg, tdk, tdv;
-    const Index kv_rows = rows/kv_group;
-    if(!make_tmap_bf16_sw128(&tk, K, kv_rows, D, BLK) || !make_tmap_bf16_sw128(&tv, V, kv_rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tq, Q, rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tdk, dK, kv_rows, D, 32)
-            || !make_tmap_bf16_sw128(&tdv, dV, kv_rows, D, 32))
-    {
-        return NNTILE_B200_E_LAUNCH;
-    }
-    static_assert(sizeof(Smem<D>) <= 232448, "Smem exceeds the 227 KB a CTA can have");
-    static const size_t smem_bytes = sizeof(Smem<D>);
-    static const cudaError_t attr = cudaFuncSetAttribute(flash_bwd_kernel<D>,
-            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-    if(attr != cudaSuccess)
-    {
-        return NNTILE_B200_E_LAUNCH;
-    }
     const float scale = 1.0f/sqrtf((float)D);
-    // Q, K, V, dO, dK, dV (bf16) and the fp32 dQ accumulator of one batch entry
-    const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
-    flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg, tdk, tdv,
-            (int)seq, (int)batch, gsz, (int)kv_group, (int)kv_batch, scale*LOG2E_F, scale, mask, sc + CLS_OFFSET, delta, lse2,
-            acc_lo, acc_hi, half_rows, reinterpret_cast<uint32_t *>(sc));
-    if(launch_status() != NNTILE_B200_OK)
+    if(aux.phases & BWD_CLASSIFY)
     {
-        return NNTILE_B200_E_LAUNCH;
+        const int st = launch_mask_classify(s, (int)seq, mask, aux.cls, aux.status);
+        if(st != NNTILE_B200_OK)
+        {
+            return st;
+        }
     }
-    bwd_dq_finish_kernel<<<grid_for(rows*D/4, 256), 256, 0, s>>>(D, rows, half_rows, scale,
-            acc_lo, acc_hi, dQ);
-    return launch_status();
+    if(aux.phases & BWD_PREP)
+    {
+        bwd_prep_kernel<<<(unsigned)((rows*(D/8) + 255)/256), 256, 0, s>>>(D, rows, aux.half_rows,
+                A, dA, lse, aux.delta, aux.lse2, aux.acc_lo, aux.acc_hi);
+        if(launch_status() != NNTILE_B200_OK)
+        {
+            return NNTILE_B200_E_LAUNCH;
+        }
+    }
+    if(aux.phases & BWD_MAIN)
+    {
+        CUtensorMap tk, tv, tq, tg, tdk, tdv;
+        const Index kv_rows = rows/kv_group;
+        if(!make_tmap_bf16_sw128(&tk, K, kv_rows, D, BLK)
+                || !make_tmap_bf16_sw128(&tv, V, kv_rows, D, BLK)
+                || !make_tmap_bf16_sw128(&tq, Q, rows, D, BLK)
+                || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK)
+                || !make_tmap_bf16_sw128(&tdk, dK, kv_rows, D, 32)
+                || !make_tmap_bf16_sw128(&tdv, dV, kv_rows, D, 32))
+        {
+            return NNTILE_B200_E_LAUNCH;
+        }
+        static_assert(sizeof(Smem<D>) <= 232448, "Smem exceeds the 227 KB a CTA can have");
+        // The opt-in to more than 48 KB of dynamic shared memory belongs to the kernel
+        // ON ONE DEVICE: a process that drives several GPUs needs it on each of them.
+        constexpr size_t smem_bytes = sizeof(Smem<D>);
+        static PerDeviceOnce optin;
+        int dev = -1;
+        if(cudaGetDevice(&dev) != cudaSuccess || !optin.ensure(dev, []() {
+                return cudaFuncSetAttribute(flash_bwd_kernel<D>,
+                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes)
+                        == cudaSuccess; }))
+        {
+            return NNTILE_B200_E_LAUNCH;
+        }
+        // Q, K, V, dO, dK, dV (bf16) and the fp32 dQ accumulator of one batch entry
+        const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
+        flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg,
+                tdk, tdv, (int)seq, (int)batch, gsz, (int)kv_group, (int)kv_batch, scale*LOG2E_F,
+                scale, mask, aux.cls, aux.delta, aux.lse2, aux.acc_lo, aux.acc_hi, aux.half_rows,
+                aux.status);
+        if(launch_status() != NNTILE_B200_OK)
+        {
+            return NNTILE_B200_E_LAUNCH;
+        }
+    }
+    if(aux.phases & BWD_FINISH)
+    {
+        bwd_dq_finish_kernel<<<grid_for(rows*D/4, 256), 256, 0, s>>>(D, rows, aux.half_rows, scale,
+                aux.acc_lo, aux.acc_hi, dQ);
+        return launch_status();
+    }
+    return NNTILE_B200_OK;
 }
 
 int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
         const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
-        const float *lse, void *scratch_dK, void *scratch_dQ, void *scratch_dV, bf16 *dK,
-        bf16 *dQ, bf16 *dV, Index kv_group, Index kv_batch)
+        const float *lse, const BwdAux &aux, bf16 *dK, bf16 *dQ, bf16 *dV, Index kv_group,
+        Index kv_batch)
 {
-    if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0)
+    if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0 || !aux.status || !aux.cls
+            || !aux.delta || !aux.lse2 || !aux.acc_lo || !aux.acc_hi)
     {
         return NNTILE_B200_E_BADARG;
     }
     return head == 128
-            ? bwd_run<128>(s, seq, batch, kv_group, kv_batch, K, Q, V, A, dA, mask, lse, scratch_dK,
-                    scratch_dQ, scratch_dV, dK, dQ, dV)
-            : bwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, V, A, dA, mask, lse, scratch_dK,
-                    scratch_dQ, scratch_dV, dK, dQ, dV);
+            ? bwd_run<128>(s, seq, batch, kv_group, kv_batch, K, Q, V, A, dA, mask, lse, aux,
+                    dK, dQ, dV)
+            : bwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, V, A, dA, mask, lse, aux,
+                    dK, dQ, dV);
 }
 
 } // namespace nb200

@@ -38,6 +38,7 @@
 // Every mbarrier wait is bounded (sm100.cuh); a wait that gives up sets a status
 // word at the start of the scratch buffer and the CTA tears down normally.
 #include "flash.cuh"
+#include "per_device.hh"
 #include "sm100.cuh"
 
 namespace nb200 {
@@ -66,9 +67,11 @@ constexpr float LN2_F = 0.6931471805599453f;
 constexpr float RESCALE_STEP = 8.0f;
 
 // ------------------------------------------------------------ mask classifier
-// grid (key block, query block), 256 threads; also clears the status word.
+// grid (key block, query block), 256 threads; also clears the status word when one
+// is given.
 __global__ void __launch_bounds__(256)
-mask_classify_kernel(int seq, int nblk, const bf16 *__restrict__ mask, uint8_t *scratch)
+mask_classify_kernel(int seq, int nblk, const bf16 *__restrict__ mask, uint8_t *cls,
+        uint32_t *status)
 {
     const int kb = blockIdx.x, qb = blockIdx.y;
     int zero = 1, ninf = 1, causal = 1;
@@ -95,11 +98,11 @@ mask_classify_kernel(int seq, int nblk, const bf16 *__restrict__ mask, uint8_t *
     causal = __syncthreads_and(causal);
     if(threadIdx.x == 0)
     {
-        scratch[CLS_OFFSET + (size_t)qb*nblk + kb] =
+        cls[(size_t)qb*nblk + kb] =
                 zero ? CLS_ZERO : ninf ? CLS_SKIP : causal ? CLS_CAUSAL : CLS_GENERIC;
-        if(kb == 0 && qb == 0)
+        if(kb == 0 && qb == 0 && status != nullptr)
         {
-            *reinterpret_cast<uint32_t *>(scratch) = 0u;
+            *status = 0u;
         }
     }
 }
@@ -192,14 +195,17 @@ __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint3
     }
 }
 
-template<int D>
+// TEST = the instantiation behind nntile_b200_test_arm_wait_timeout: waits give up
+// after WAIT_LIMIT_TEST_NS and the producer withholds its first K copy, so that one
+// wait runs out and the failure report can be checked.  Never launched otherwise.
+template<int D, bool TEST>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
         const __grid_constant__ CUtensorMap tmap_a,
         int seq, int batch, int gsz, int kv_group, int kv_batch, float scale_log2,
-        const bf16 *__restrict__ mask,
-        uint8_t *scratch, float *__restrict__ lse, bf16 *__restrict__ A)
+        const bf16 *__restrict__ mask, uint32_t *status, const uint8_t *__restrict__ cls_tab,
+        float *__restrict__ lse, bf16 *__restrict__ A)
 {
     extern __shared__ uint8_t smem_raw[];
     Smem<D> &sm = *reinterpret_cast<Smem<D> *>(
@@ -212,8 +218,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int pair = npairs - 1 - unit;                         // heavy (late) rows first
     const int qb0 = 2*pair, qb1 = 2*pair + 1;
     const bool has1 = qb1 < nblk;
-    const uint8_t *cls_tab = scratch + CLS_OFFSET;
     volatile uint32_t *abort_flag = &sm.abort_flag;
+    constexpr uint64_t LIMIT = TEST ? WAIT_LIMIT_TEST_NS : WAIT_LIMIT_NS;
 
     // ---- set-up: barriers, TMEM, list of key blocks ---------------------------
     if(tid == 0)
@@ -254,7 +260,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if(warp == 2 && lane == 0)
     {
         // a CTA of this launch that gave up earlier tells the others to skip their work
-        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(scratch) != 0u ? 1u : 0u;
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t *>(status) != 0u ? 1u : 0u;
     }
     if(warp == 3)
     {
@@ -319,18 +325,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const int st = it % KV_STAGES;
                 const uint32_t ph = (uint32_t)(it/KV_STAGES) & 1u;
                 const int krow = kv_row_base + (int)sm.list[it]*BLK;
-                ok = mbar_wait(&sm.k_empty[st], ph ^ 1u, abort_flag);
+                ok = mbar_wait<LIMIT>(&sm.k_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
-                mbar_arrive_expect_tx(&sm.k_full[st], TILE_BYTES);
-                load_tile<D>(sm.k[st], &tmap_k, &sm.k_full[st], krow);
-                ok = mbar_wait(&sm.v_empty[st], ph ^ 1u, abort_flag);
+                if(!(TEST && it == 0))
+                {
+                    mbar_arrive_expect_tx(&sm.k_full[st], TILE_BYTES);
+                    load_tile<D>(sm.k[st], &tmap_k, &sm.k_full[st], krow);
+                }
+                ok = mbar_wait<LIMIT>(&sm.v_empty[st], ph ^ 1u, abort_flag);
                 if(!ok) break;
                 mbar_arrive_expect_tx(&sm.v_full[st], TILE_BYTES);
                 load_tile<D>(sm.v[st], &tmap_v, &sm.v_full[st], krow);
             }
             if(!ok)
             {
-                atomicExch(reinterpret_cast<uint32_t *>(scratch), 1u);
+                atomicCAS(status, 0u, STATUS_FWD_PRODUCER);
             }
         }
     }
@@ -361,7 +370,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             {
                 if(nact_r[t] > 0)
                 {
-                    ok = mbar_wait(&sm.q_full[t], 0, abort_flag);
+                    ok = mbar_wait<LIMIT>(&sm.q_full[t], 0, abort_flag);
                 }
             }
             // cls_other: class of the same block for the other tile
@@ -370,7 +379,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const int st = it % KV_STAGES;
                 if(it > k_waited)
                 {
-                    if(!mbar_wait(&sm.k_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag))
+                    if(!mbar_wait<LIMIT>(&sm.k_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag))
                     {
                         return false;
                     }
@@ -409,7 +418,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                 }
                 if(!ok) break;
-                ok = mbar_wait(&sm.v_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag);
+                ok = mbar_wait<LIMIT>(&sm.v_full[st], (uint32_t)(it/KV_STAGES) & 1u, abort_flag);
                 const int last_t = cur[1] != CLS_SKIP ? 1 : 0;
                 const uint32_t v_lo = v_lo0 + (uint32_t)st*STAGE_LO;
     #pragma unroll
@@ -422,7 +431,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     PROF_T(mt0);
                     PROF_T(mt1);
                     PROF_T(mt2);
-                    ok = mbar_wait(&sm.p_full[t], p_phase[t], abort_flag);
+                    ok = mbar_wait<LIMIT>(&sm.p_full[t], p_phase[t], abort_flag);
                     if(!ok) break;
                     p_phase[t] ^= 1u;
                     tc_fence_after_sync();
@@ -456,7 +465,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             if(!ok)
             {
-                atomicExch(reinterpret_cast<uint32_t *>(scratch), 2u);
+                atomicCAS(status, 0u, STATUS_FWD_MMA);
             }
         }
     }
@@ -491,7 +500,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 continue;
             }
             PROF_T(pt0);
-            ok = mbar_wait(&sm.s_full[t], s_phase, abort_flag);
+            ok = mbar_wait<LIMIT>(&sm.s_full[t], s_phase, abort_flag);
             if(!ok) break;
             s_phase ^= 1u;
             tc_fence_after_sync();
@@ -635,7 +644,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // ---- epilogue: normalise, merge with the stored (lse, A), store ---------
         if(ok && nact > 0)
         {
-            ok = mbar_wait(&sm.o_full[t], 0, abort_flag);
+            ok = mbar_wait<LIMIT>(&sm.o_full[t], 0, abort_flag);
         }
         ok = __all_sync(0xffffffffu, ok);     // the epilogue is warp-collective
         if(ok && nact > 0)
@@ -772,7 +781,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         if(!ok && lane == 0)
         {
-            atomicExch(reinterpret_cast<uint32_t *>(scratch), 3u);
+            atomicCAS(status, 0u, STATUS_FWD_SOFTMAX);
         }
     }
     // ---- tear-down ---------------------------------------------------------------
@@ -780,10 +789,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     {
         // the Q copies issued at the start must have landed before the shared memory
         // goes away, also when nobody needed them
-        mbar_wait(&sm.q_full[0], 0, abort_flag);
+        mbar_wait<LIMIT>(&sm.q_full[0], 0, abort_flag);
         if(has1)
         {
-            mbar_wait(&sm.q_full[1], 0, abort_flag);
+            mbar_wait<LIMIT>(&sm.q_full[1], 0, abort_flag);
         }
     }
     if(*abort_flag != 0u && tid == 0)
@@ -824,10 +833,12 @@ bool flash_fwd_sm100_supports(Index seq, Index head, Index batch)
             && batch*seq < ((Index)1 << 31) && batch*((seq/fwd::BLK + 1)/2) < ((Index)1 << 31);
 }
 
+static std::atomic<uint32_t> g_wait_test_armed{0};
+
 template<int D>
 static int fwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index kv_batch,
         const bf16 *K, const bf16 *Q,
-        const bf16 *mask, const bf16 *V, float *lse, bf16 *A, uint8_t *scratch)
+        const bf16 *mask, const bf16 *V, float *lse, bf16 *A, const FwdAux &aux)
 {
     using namespace fwd;
     CUtensorMap tq, tk, tv, ta;
@@ -840,14 +851,20 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index
         return NNTILE_B200_E_LAUNCH;
     }
     const int nblk = (int)(seq/BLK);
-    if(launch_mask_classify(s, (int)seq, mask, scratch) != NNTILE_B200_OK)
+    if(aux.classify && launch_mask_classify(s, (int)seq, mask, aux.cls, aux.status) != NNTILE_B200_OK)
     {
         return NNTILE_B200_E_LAUNCH;
     }
-    static const size_t smem_bytes = sizeof(Smem<D>) + 1024;
-    static const cudaError_t attr = cudaFuncSetAttribute(flash_fwd_kernel<D>,
-            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-    if(attr != cudaSuccess)
+    // The opt-in to more than 48 KB of dynamic shared memory belongs to the kernel
+    // ON ONE DEVICE: a process that drives several GPUs needs it on each of them.
+    constexpr size_t smem_bytes = sizeof(Smem<D>) + 1024;
+    static PerDeviceOnce optin;
+    int dev = -1;
+    if(cudaGetDevice(&dev) != cudaSuccess || !optin.ensure(dev, []() {
+            return cudaFuncSetAttribute(flash_fwd_kernel<D, false>,
+                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) == cudaSuccess
+                && cudaFuncSetAttribute(flash_fwd_kernel<D, true>,
+                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) == cudaSuccess; }))
     {
         return NNTILE_B200_E_LAUNCH;
     }
@@ -855,35 +872,44 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index
     const float scale_log2 = LOG2E_F/sqrtf((float)D);
     // Q, K, V, A of one batch entry
     const int gsz = l2_group_size(batch, (size_t)seq*D*2*4);
-    flash_fwd_kernel<D><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, ta, (int)seq, (int)batch, gsz,
-            (int)kv_group, (int)kv_batch, scale_log2, mask, scratch, lse, A);
+    if(g_wait_test_armed.exchange(0u, std::memory_order_relaxed) != 0u)
+    {
+        flash_fwd_kernel<D, true><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, ta, (int)seq,
+                (int)batch, gsz, (int)kv_group, (int)kv_batch, scale_log2, mask, aux.status,
+                aux.cls, lse, A);
+        return launch_status();
+    }
+    flash_fwd_kernel<D, false><<<grid, THREADS, smem_bytes, s>>>(tq, tk, tv, ta, (int)seq,
+            (int)batch, gsz, (int)kv_group, (int)kv_batch, scale_log2, mask, aux.status, aux.cls,
+            lse, A);
     return launch_status();
 }
 
-int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *scratch)
+int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *cls,
+        uint32_t *status)
 {
     const int nblk = seq/fwd::BLK;
-    fwd::mask_classify_kernel<<<dim3(nblk, nblk), 256, 0, s>>>(seq, nblk, mask, scratch);
+    fwd::mask_classify_kernel<<<dim3(nblk, nblk), 256, 0, s>>>(seq, nblk, mask, cls, status);
     return launch_status();
 }
 
 int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A, void *scratch,
-        size_t scratch_bytes, Index kv_group, Index kv_batch)
+        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A, const FwdAux &aux,
+        Index kv_group, Index kv_batch)
 {
-    if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0)
+    if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0 || !aux.status || !aux.cls)
     {
         return NNTILE_B200_E_BADARG;
     }
-    const size_t nblk = (size_t)(seq/fwd::BLK);
-    if(scratch_bytes < CLS_OFFSET + nblk*nblk)
-    {
-        return NNTILE_B200_E_SCRATCH;
-    }
-    uint8_t *sc = static_cast<uint8_t *>(scratch);
     return head == 128
-            ? fwd_run<128>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, sc)
-            : fwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, sc);
+            ? fwd_run<128>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, aux)
+            : fwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, aux);
 }
 
 } // namespace nb200
+
+// Test support: arms the one-shot wait-timeout hook described in the header.
+extern "C" void nntile_b200_test_arm_wait_timeout(void)
+{
+    nb200::g_wait_test_armed.store(1u, std::memory_order_relaxed);
+}

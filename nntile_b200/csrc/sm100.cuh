@@ -65,11 +65,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return done != 0;
 }
 
-// Every wait in these kernels is bounded: it gives up after WAIT_LIMIT_NS of
-// wall time, or as soon as a sibling role has given up (`*abort_flag` set), and
-// returns false; the caller records where it stopped and leaves its loop, and
-// the CTA tears down normally.  A wait never spins forever and never traps.
+// Every wait in these kernels is bounded: it gives up after LIMIT_NS of wall time,
+// or as soon as a sibling role has given up (`*abort_flag` set), and returns
+// false; the caller records where it stopped and leaves its loop, and the CTA
+// tears down normally.  A wait never spins forever and never traps.  The limit is
+// a compile-time constant (the issuing threads have no register to spare for
+// it); the test instantiation of the forward kernel uses WAIT_LIMIT_TEST_NS.
 constexpr uint64_t WAIT_LIMIT_NS = 200ull*1000ull*1000ull;
+constexpr uint64_t WAIT_LIMIT_TEST_NS = 1000ull*1000ull;
 
 __device__ __forceinline__ uint64_t global_timer_ns()
 {
@@ -78,6 +81,7 @@ __device__ __forceinline__ uint64_t global_timer_ns()
     return t;
 }
 
+template<uint64_t LIMIT_NS = WAIT_LIMIT_NS>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
         volatile uint32_t *abort_flag)
 {
@@ -100,7 +104,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
         {
             return false;
         }
-        if(global_timer_ns() - t0 > WAIT_LIMIT_NS)
+        if(global_timer_ns() - t0 > LIMIT_NS)
         {
             *abort_flag = 1u;
             return false;
@@ -396,9 +400,7 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthread
 
 __device__ __forceinline__ void red_add_f32(float *addr, float a)
 {
-#ifndef NB200_EXP_NORED      // timing experiment only: results are wrong without it
     asm volatile("red.global.add.f32 [%0], %1;" :: "l"(addr), "f"(a) : "memory");
-#endif
 }
 
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d)

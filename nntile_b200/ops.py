@@ -95,27 +95,47 @@ def accumulate_attn_output(head, seq, batch, src_lse, src_attn, dst_lse, dst_att
 
 def gemm(transA, transB, m, n, k, batch, alpha, A, B, beta, C):
     """Batched column-major C = alpha*op(A)*op(B) + beta*C with packed leading
-    dimensions - the contract of nntile::kernel::cublas::gemm<T>
-    (src/kernel/cublas.cc:35-164).  A library GEMM in the reference and here:
-    cuBLAS through torch.baddbmm, fp32 accumulation, no TF32."""
-    # a column-major p-by-q matrix is a row-major (q, p) torch matrix
-    a = A.view(batch, m, k) if transA else A.view(batch, k, m)
-    b = B.view(batch, k, n) if transB else B.view(batch, n, k)
-    c = C.view(batch, n, m)
-    # C^T = op(B)^T op(A)^T
-    bt = b.transpose(1, 2) if transB else b
-    at = a.transpose(1, 2) if transA else a
+    dimensions - the contract and argument order of nntile::kernel::cublas::gemm<T>
+    (src/kernel/cublas.cc:35-164), through the C ABI.  A library GEMM in the
+    reference and here (cublasGemmStridedBatchedEx, fp32 compute, no TF32); the
+    handle is torch's cuBLAS handle for the current stream, the stand-in for the
+    StarPU worker's handle."""
     prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False     # the handle's math mode follows this
     try:
-        if beta == 0.0:
-            torch.bmm(bt, at, out=c)
-            if alpha != 1.0:
-                c.mul_(alpha)
-        else:
-            torch.baddbmm(c, bt, at, beta=float(beta), alpha=float(alpha), out=c)
+        handle = torch.cuda.current_blas_handle()
+        _call(f"nntile_b200_gemm_{_sfx(C)}", ctypes.c_void_p(handle), int(bool(transA)),
+              int(bool(transB)), m, n, k, batch, float(alpha), _ptr(A), _ptr(B), float(beta),
+              _ptr(C))
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def transpose_rope(lead, head, seq, batch, sin, cos, src, dst):
+    """dst[head, seq, batch, lead] = RoPE(src[lead, head, seq, batch]); sin = cos = None
+    changes the layout only."""
+    _call("nntile_b200_transpose_rope_bf16", _stream(), lead, head, seq, batch, _ptr(sin),
+          _ptr(cos), _ptr(src), _ptr(dst))
+
+
+def transpose_bias(lead, head, seq, batch, bias, src, dst):
+    """dst[head, seq, batch, lead] = src[lead, head, seq, batch] + bias[head, lead]."""
+    _call("nntile_b200_transpose_bias_bf16", _stream(), lead, head, seq, batch, _ptr(bias),
+          _ptr(src), _ptr(dst))
+
+
+def transpose_heads_back(lead, head, seq, batch, src, dst):
+    """dst[lead, head, seq, batch] = src[head, seq, batch, lead]."""
+    _call("nntile_b200_transpose_heads_back_bf16", _stream(), lead, head, seq, batch,
+          _ptr(src), _ptr(dst))
+
+
+def flash_sdpa_read_status(scratch) -> int:
+    """Status word of the tcgen05 kernels kept at the start of `scratch`
+    (synchronises the current stream)."""
+    code = ctypes.c_uint(0)
+    _call("nntile_b200_flash_sdpa_read_status", _stream(), _ptr(scratch), ctypes.byref(code))
+    return int(code.value)
 
 
 def flash_sdpa_fwd(seq, head, batch, K, Q, mask, scratch_lse, V, scratch_A, lse, A):

@@ -82,74 +82,191 @@ def _i64arr(vals):
     return (ctypes.c_int64*len(vals))(*[int(v) for v in vals])
 
 
-def flash_sdpa_fwd_async(K, Q, mask, lse, V, A, seq_tile=None, batch_tile=None):
+def _tensor_call(name, shape5, base5, tiled, scratch_holder=None):
+    """Run one tensor-level C entry point on lists of TiledBuffer."""
+    lib = _lib.load()
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(_i64arr(shape5), _i64arr(base5))
+    dev = tiled[0].tiles[0].device
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    keep = [t.pointers() for t in tiled]
+    st = getattr(lib, name)(
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), _i64arr(shape5),
+        _i64arr(base5), *[ctypes.cast(p, ctypes.POINTER(ctypes.c_void_p)) for p in keep],
+        ctypes.c_void_p(scratch.data_ptr()), nbytes)
+    _lib.check(name, st)
+    if scratch_holder is not None:
+        scratch_holder.append(scratch)
+    return scratch
+
+
+def flash_sdpa_fwd_async(K, Q, mask, lse, V, A, seq_tile=None, batch_tile=None, scratch_out=None):
     """nntile.functions.flash_sdpa_fwd_cudnn_async on whole tensors: cuts them into
     tiles like the reference's traits do, runs the C tensor-level loops, gathers A
-    and lse back in place.  K, Q, V, A: (H, G, B, S, D) bf16; mask: additive
-    (Sq, Sk) bf16 buffer = Fortran [Sk, Sq]; lse: (H, G, B, S) fp32."""
+    and lse back in place.  Q, A: (H, G, B, S, D) bf16; K, V: the same shape, or
+    (H, B, S, D) = [head, seq, batch, kv_heads] not replicated over the group
+    (grouped-query form); mask: additive (Sq, Sk) bf16 buffer = Fortran [Sk, Sq];
+    lse: (H, G, B, S) fp32."""
     H, G, B, S, D = Q.shape
+    gqa = K.dim() == 4
     seq_tile = seq_tile or S
     bt = tuple(batch_tile or (B, G, H))
     base5 = (D, seq_tile) + bt
-    tK, tQ, tV, tA = (TiledBuffer(x, base5) for x in (K, Q, V, A))
+    kv_base = (D, seq_tile, bt[0], bt[2]) if gqa else base5
+    tK, tV = TiledBuffer(K, kv_base), TiledBuffer(V, kv_base)
+    tQ, tA = TiledBuffer(Q, base5), TiledBuffer(A, base5)
     tM = TiledBuffer(mask, (seq_tile, seq_tile))
     tL = TiledBuffer(lse, (seq_tile,) + bt)
-    lib = _lib.load()
-    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(_i64arr(base5))
-    scratch = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
-    keep = [tK.pointers(), tQ.pointers(), tM.pointers(), tL.pointers(), tV.pointers(),
-            tA.pointers()]
-    st = lib.nntile_b200_tensor_flash_sdpa_fwd_bf16(
-        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), _i64arr((D, S, B, G, H)),
-        _i64arr(base5), *[ctypes.cast(p, ctypes.POINTER(ctypes.c_void_p)) for p in keep],
-        ctypes.c_void_p(scratch.data_ptr()), nbytes)
-    _lib.check("nntile_b200_tensor_flash_sdpa_fwd_bf16", st)
+    name = "nntile_b200_tensor_flash_sdpa_fwd_gqa_bf16" if gqa \
+        else "nntile_b200_tensor_flash_sdpa_fwd_bf16"
+    _tensor_call(name, (D, S, B, G, H), base5, [tK, tQ, tM, tL, tV, tA], scratch_out)
     A.copy_(tA.gather())
     lse.copy_(tL.gather())
 
 
 def flash_sdpa_bwd_async(K, Q, V, A, dA, mask, lse, dK, dQ, dV, seq_tile=None,
-                         batch_tile=None):
-    """nntile.functions.flash_sdpa_bwd_cudnn_async on whole tensors."""
+                         batch_tile=None, scratch_out=None):
+    """nntile.functions.flash_sdpa_bwd_cudnn_async on whole tensors (K, V, dK, dV
+    5-D like Q, or 4-D un-replicated for the grouped-query form)."""
     H, G, B, S, D = Q.shape
+    gqa = K.dim() == 4
     seq_tile = seq_tile or S
     bt = tuple(batch_tile or (B, G, H))
     base5 = (D, seq_tile) + bt
-    tK, tQ, tV, tA, tdA, tdK, tdQ, tdV = (TiledBuffer(x, base5)
-                                          for x in (K, Q, V, A, dA, dK, dQ, dV))
+    kv_base = (D, seq_tile, bt[0], bt[2]) if gqa else base5
+    tK, tV, tdK, tdV = (TiledBuffer(x, kv_base) for x in (K, V, dK, dV))
+    tQ, tA, tdA, tdQ = (TiledBuffer(x, base5) for x in (Q, A, dA, dQ))
     tM = TiledBuffer(mask, (seq_tile, seq_tile))
     tL = TiledBuffer(lse, (seq_tile,) + bt)
-    lib = _lib.load()
-    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(_i64arr(base5))
-    scratch = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
-    keep = [t.pointers() for t in (tK, tQ, tV, tA, tdA, tM, tL, tdK, tdQ, tdV)]
-    st = lib.nntile_b200_tensor_flash_sdpa_bwd_bf16(
-        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), _i64arr((D, S, B, G, H)),
-        _i64arr(base5), *[ctypes.cast(p, ctypes.POINTER(ctypes.c_void_p)) for p in keep],
-        ctypes.c_void_p(scratch.data_ptr()), nbytes)
-    _lib.check("nntile_b200_tensor_flash_sdpa_bwd_bf16", st)
+    name = "nntile_b200_tensor_flash_sdpa_bwd_gqa_bf16" if gqa \
+        else "nntile_b200_tensor_flash_sdpa_bwd_bf16"
+    _tensor_call(name, (D, S, B, G, H), base5, [tK, tQ, tV, tA, tdA, tM, tL, tdK, tdQ, tdV],
+                 scratch_out)
     dK.copy_(tdK.gather())
     dQ.copy_(tdQ.gather())
     dV.copy_(tdV.gather())
 
 
-class Sdpa:
-    """Mirror of nntile.layer.Sdpa on single-tile tensors (or, for the fused
-    path, tensors tiled along sequence and batch axes).
+class _TiledChain:
+    """Tile loops of the unfused chain: what nntile::tensor::gemm_async
+    (src/tensor/gemm.cc:344-410: every output tile, contraction tiles accumulated
+    with beta = 1 after the first), maxsumexp_async (src/tensor/maxsumexp.cc:80-107:
+    the K tiles of a fibre accumulate into the same (max, sum) pair),
+    softmax_inplace_async (src/tensor/softmax_inplace.cc:80-112), mask_scalar_async
+    (src/tensor/mask_scalar.cc:26-62), sumprod_slice_async, add_slice_inplace_async
+    and multiply_inplace_async do on tiled tensors, in the order
+    nntile.layer.Sdpa issues them (sdpa.py:407-455, 595-698).  Tensors are cut along
+    the sequence axis (queries and keys separately) and the three batch axes; the
+    head axis is one tile."""
 
-    q, k, v: (H, G, B, S, D) buffers.  ``mask``: for the unfused chain a bool
-    (Sq, Sk) buffer = Fortran [Sk, Sq] (true = keep); for the fused path the
-    additive mask in the tensors' dtype (0 / -inf), as sdpa.py:457-531 prepares.
+    def __init__(self, layer, q_tile, k_tile, batch_tile):
+        self.L = layer
+        H, G, B, Sq, D = layer.q.shape
+        Sk = layer.k.shape[3]
+        self.bt = tuple(batch_tile or (B, G, H))
+        self.qt, self.kt = int(q_tile or Sq), int(k_tile or Sk)
+        self.D, self.Sq, self.Sk = D, Sq, Sk
+        self.nq, self.nk = -(-Sq//self.qt), -(-Sk//self.kt)
+        self.nb = tuple(-(-s//t) for s, t in zip((B, G, H), self.bt))
+        self.batch_tiles = self.nb[0]*self.nb[1]*self.nb[2]
+        dev, dt = layer.q.device, layer.q.dtype
+        self.attn_full = torch.empty((H, G, B, Sq, Sk), dtype=dt, device=dev)
+        self.attn = TiledBuffer(self.attn_full, (self.kt, self.qt) + self.bt)
+        self.mse = TiledBuffer(torch.empty((H, G, B, Sq, 2), dtype=dt, device=dev),
+                               (2, self.qt) + self.bt)
+        self.sps = TiledBuffer(torch.empty((H, G, B, Sq), dtype=dt, device=dev),
+                               (self.qt,) + self.bt)
+        self.mask = None if layer.mask is None else TiledBuffer(layer.mask, (self.kt, self.qt))
+
+    def _cut(self, x, seq_tile):
+        return TiledBuffer(x, (self.D, seq_tile) + self.bt)
+
+    @staticmethod
+    def _nbatch(t):
+        return t.shape[0]*t.shape[1]*t.shape[2]
+
+    def forward(self):
+        L = self.L
+        q, k, v = self._cut(L.q, self.qt), self._cut(L.k, self.kt), self._cut(L.v, self.kt)
+        y = self._cut(L.y, self.qt)
+        nq, nk = self.nq, self.nk
+        for b in range(self.batch_tiles):
+            for qi in range(nq):
+                tq, ty, tm = q.tiles[qi + nq*b], y.tiles[qi + nq*b], self.mse.tiles[qi + nq*b]
+                nbat, sq = self._nbatch(tq), tq.shape[3]
+                ops.clear(tm)
+                for ki in range(nk):
+                    tk = k.tiles[ki + nk*b]
+                    ta = self.attn.tiles[ki + nk*(qi + nq*b)]
+                    sk = tk.shape[3]
+                    ops.gemm(True, False, sk, sq, self.D, nbat, L.scale, tk, tq, 0.0, ta)
+                    if self.mask is not None:
+                        ops.mask_scalar(sk*sq, nbat, self.mask.tiles[ki + nk*qi], L.val, ta)
+                    ops.maxsumexp(1, sq*nbat, sk, ta, tm)
+                for ki in range(nk):
+                    ta = self.attn.tiles[ki + nk*(qi + nq*b)]
+                    sk = ta.shape[4]
+                    ops.softmax_inplace(1, sq*nbat, sk, tm, 1.0, ta)
+                    ops.gemm(False, False, self.D, sq, sk, nbat, 1.0, v.tiles[ki + nk*b], ta,
+                             0.0 if ki == 0 else 1.0, ty)
+        L.y.copy_(y.gather())
+        L.attn = self.attn.gather()
+        L.attn_maxsumexp = self.mse.gather()
+
+    def backward(self, dy, dq, dk, dv):
+        L = self.L
+        q, k, v = self._cut(L.q, self.qt), self._cut(L.k, self.kt), self._cut(L.v, self.kt)
+        y, tdy = self._cut(L.y, self.qt), self._cut(dy, self.qt)
+        tdq, tdk, tdv = self._cut(dq, self.qt), self._cut(dk, self.kt), self._cut(dv, self.kt)
+        nq, nk = self.nq, self.nk
+        for b in range(self.batch_tiles):
+            for qi in range(nq):
+                tq, ty, tg = q.tiles[qi + nq*b], y.tiles[qi + nq*b], tdy.tiles[qi + nq*b]
+                tsp = self.sps.tiles[qi + nq*b]
+                nbat, sq = self._nbatch(tq), tq.shape[3]
+                ops.sumprod_slice(1, sq*nbat, self.D, 1.0, ty, tg, 0.0, tsp)
+                for ki in range(nk):
+                    tk, tv = k.tiles[ki + nk*b], v.tiles[ki + nk*b]
+                    ta = self.attn.tiles[ki + nk*(qi + nq*b)]
+                    sk = tk.shape[3]
+                    da = torch.empty_like(ta)
+                    ops.gemm(True, False, sk, sq, self.D, nbat, 1.0, tv, tg, 0.0, da)
+                    ops.gemm(False, True, self.D, sk, sq, nbat, 1.0, tg, ta, 1.0,
+                             tdv.tiles[ki + nk*b])
+                    ops.add_slice_inplace(1, sq*nbat, sk, -1.0, tsp, 1.0, da)
+                    ops.multiply_inplace(da.numel(), 1.0, ta, da)
+                    if self.mask is not None:
+                        ops.mask_scalar(sk*sq, nbat, self.mask.tiles[ki + nk*qi], 0.0, da)
+                    ops.gemm(False, True, self.D, sk, sq, nbat, L.scale, tq, da, 1.0,
+                             tdk.tiles[ki + nk*b])
+                    ops.gemm(False, False, self.D, sq, sk, nbat, L.scale, tk, da, 1.0,
+                             tdq.tiles[qi + nq*b])
+        dq.copy_(tdq.gather())
+        dk.copy_(tdk.gather())
+        dv.copy_(tdv.gather())
+
+
+class Sdpa:
+    """Mirror of nntile.layer.Sdpa on tensors that are one tile or are cut along
+    the sequence and batch axes (``seq_tile`` for queries and keys alike, or
+    ``q_tile`` / ``k_tile`` separately for the unfused chain; ``batch_tile`` =
+    (batch, group, kv_heads) extents of a tile).
+
+    q, k, v: (H, G, B, S, D) buffers; for the fused path k and v may also be
+    (H, B, S, D), not replicated over the group (grouped-query form).  ``mask``:
+    for the unfused chain a bool (Sq, Sk) buffer = Fortran [Sk, Sq] (true = keep);
+    for the fused path the additive mask in the tensors' dtype (0 / -inf), as
+    sdpa.py:457-531 prepares.
     """
 
     def __init__(self, q, k, v, mask=None, flash_attention=False, seq_tile=None,
-                 batch_tile=None):
+                 batch_tile=None, q_tile=None, k_tile=None):
         self.q, self.k, self.v, self.mask = q, k, v, mask
         self.flash_attention = flash_attention
         self.seq_tile, self.batch_tile = seq_tile, batch_tile
+        self.q_tile, self.k_tile = q_tile or seq_tile, k_tile or seq_tile
         H, G, B, S, D = q.shape
         self.head, self.n_seq = D, S
-        self.n_seq_k = k.shape[3]
+        self.n_seq_k = k.shape[-2]
         self.batch = H*G*B
         self.scale = sdpa_scale(D)
         self.val = -math.inf
@@ -162,10 +279,18 @@ class Sdpa:
             self.flash_logsumexp = torch.empty((H, G, B, S), dtype=torch.float32, device=dev)
             if mask is None:
                 self.mask = torch.zeros((S, S), dtype=dt, device=dev)
+        elif self._tiled():
+            self._chain = _TiledChain(self, self.q_tile, self.k_tile, batch_tile)
         else:
             self.attn = torch.empty((H, G, B, S, self.n_seq_k), dtype=dt, device=dev)
             self.attn_maxsumexp = torch.empty((H, G, B, S, 2), dtype=dt, device=dev)
             self.attn_sumprod_slice = torch.empty((H, G, B, S), dtype=dt, device=dev)
+
+    def _tiled(self) -> bool:
+        H, G, B, S, D = self.q.shape
+        return bool((self.q_tile and self.q_tile < S)
+                    or (self.k_tile and self.k_tile < self.n_seq_k)
+                    or (self.batch_tile and tuple(self.batch_tile) != (B, G, H)))
 
     # ---- forward ----------------------------------------------------------
     def forward_async(self):
@@ -174,6 +299,9 @@ class Sdpa:
             ops.clear(self.y)                                   # sdpa.py:539
             flash_sdpa_fwd_async(self.k, self.q, self.mask, self.flash_logsumexp, self.v,
                                  self.y, self.seq_tile, self.batch_tile)
+            return self.y
+        if self._tiled():
+            self._chain.forward()
             return self.y
         D, Sq, Sk, nb = self.head, self.n_seq, self.n_seq_k, self.batch
         ops.gemm(True, False, Sk, Sq, D, nb, self.scale, self.k, self.q, 0.0, self.attn)
@@ -225,6 +353,9 @@ class Sdpa:
             flash_sdpa_bwd_async(self.k, self.q, self.v, self.y, dy, self.mask,
                                  self.flash_logsumexp, dk, dq, dv, self.seq_tile,
                                  self.batch_tile)
+            return
+        if self._tiled():
+            self._chain.backward(dy, dq, dk, dv)
             return
         D, Sq, Sk, nb = self.head, self.n_seq, self.n_seq_k, self.batch
         dattn = torch.empty_like(self.attn)

@@ -59,6 +59,26 @@ def have_ref() -> bool:
     return ref is not None
 
 
+def ref_gpu():
+    """The reference's own GPU wrappers of the fused pair (cuDNN graph + merge /
+    add_inplace kernels, oracle/_ref_gpu), loaded on demand; None when the library
+    was not built or cuDNN cannot be loaded.  Needs a GPU to call."""
+    global _ref_gpu
+    if _ref_gpu is False:
+        try:
+            _ref_gpu = _load(_build.REF_GPU_SO)
+        except OSError:
+            _ref_gpu = None
+        if _ref_gpu is not None:
+            vp, i64 = ctypes.c_void_p, ctypes.c_int64
+            _ref_gpu.refgpu_flash_sdpa_fwd_bf16.argtypes = [vp, i64, i64, i64] + [vp]*8
+            _ref_gpu.refgpu_flash_sdpa_bwd_bf16.argtypes = [vp, i64, i64, i64] + [vp]*13
+    return _ref_gpu
+
+
+_ref_gpu = False
+
+
 def _p(a: np.ndarray):
     assert a.flags.f_contiguous or a.flags.c_contiguous
     return _vp(a.ctypes.data)
@@ -181,6 +201,63 @@ def accumulate_attn_output(head, seq, batch, src_lse, src_attn, dst_lse, dst_att
         _fn("port", "accumulate_attn_output", _sfx(dst_attn))(
             _i64(head), _i64(seq), _i64(batch), _p(src_lse), _p(src_attn),
             _p(dst_lse), _p(dst_attn), ctypes.c_int(1 if cuda_rules else 0))
+
+
+def transpose(m, n, alpha, src, dst, backend="port"):
+    """dst[i*n + j] = alpha*src[i + j*m] (include/nntile/kernel/transpose/cpu.hh:24)."""
+    _fn(backend, "transpose", _sfx(dst))(_i64(m), _i64(n), _f32(alpha), _p(src), _p(dst))
+
+
+def rope(m, n, sin, cos, src, dst, backend="port"):
+    """include/nntile/kernel/rope/cpu.hh:23."""
+    _fn(backend, "rope", _sfx(dst))(_i64(m), _i64(n), _p(sin), _p(cos), _p(src), _p(dst))
+
+
+def add_fiber_inplace(m, n, k, batch, alpha, src, beta, dst, backend="port"):
+    """include/nntile/kernel/add_fiber_inplace/cpu.hh:24."""
+    _fn(backend, "add_fiber_inplace", _sfx(dst))(_i64(m), _i64(n), _i64(k), _i64(batch),
+                                                 _f32(alpha), _p(src), _f32(beta), _p(dst))
+
+
+def rope_sin_cos(head, positions, theta=10000.0):
+    """sin, cos float32 [head/2, seq, batch] as LlamaAttention._fill_sin_cos builds
+    them (wrappers/python/nntile/model/llama_attention.py:1122-1134); `positions`
+    is [batch, seq]."""
+    tmp = np.arange(0, head, 2, dtype=np.float32)
+    inv_freq = 1.0/(theta**(tmp/head))
+    frame = np.empty((head//2, positions.shape[1], positions.shape[0]))
+    for i in range(positions.shape[0]):
+        frame[:, :, i] = np.outer(inv_freq, positions[i, :])
+    return (np.sin(frame).astype(np.float32, order="F"),
+            np.cos(frame).astype(np.float32, order="F"))
+
+
+def attention_prologue(proj, sin=None, cos=None, bias=None, backend="port"):
+    """What the reference's attention layers run between a projection and the SDPA
+    layer: transpose_async of [lead..., head, seq, batch] into [head, seq, batch,
+    lead...] (the lead axes flattened here), then rope_async (Llama,
+    llama_attention.py:592-610) or add_fiber_inplace_async of a [head, lead] bias
+    (GPT-2, gpt2_attention.py:258-269).  `proj` is a Fortran array
+    [lead, head, seq, batch]; returns [head, seq, batch, lead]."""
+    lead, head, seq, batch = proj.shape
+    out = zeros((head, seq, batch, lead), proj.dtype)
+    transpose(lead, head*seq*batch, 1.0, proj, out, backend=backend)
+    if sin is not None:
+        rot = zeros(out.shape, proj.dtype)
+        rope((head//2)*seq*batch, lead, sin, cos, out, rot, backend=backend)
+        out = rot
+    if bias is not None:
+        add_fiber_inplace(1, seq*batch, head, lead, 1.0, bias, 1.0, out, backend=backend)
+    return out
+
+
+def attention_epilogue(attn, backend="port"):
+    """transpose_async(1.0, A, At, 3) behind the SDPA layer (llama_attention.py:
+    620-623): [head, seq, batch, lead] -> [lead, head, seq, batch]."""
+    head, seq, batch, lead = attn.shape
+    out = zeros((lead, head, seq, batch), attn.dtype)
+    transpose(head*seq*batch, lead, 1.0, attn, out, backend=backend)
+    return out
 
 
 def flash_sdpa_fwd_tile(seq, head, batch, K, Q, mask, V, lse, A):

@@ -12,14 +12,17 @@
 #include <nntile/base_types.hh>
 #include <nntile/constants.hh>
 #include <nntile/kernel/accumulate_attn_output/cpu.hh>
+#include <nntile/kernel/add_fiber_inplace/cpu.hh>
 #include <nntile/kernel/add_inplace/cpu.hh>
 #include <nntile/kernel/add_slice_inplace/cpu.hh>
 #include <nntile/kernel/cblas.hh>
 #include <nntile/kernel/mask_scalar/cpu.hh>
 #include <nntile/kernel/maxsumexp/cpu.hh>
 #include <nntile/kernel/multiply_inplace/cpu.hh>
+#include <nntile/kernel/rope/cpu.hh>
 #include <nntile/kernel/softmax_inplace/cpu.hh>
 #include <nntile/kernel/sumprod_slice/cpu.hh>
+#include <nntile/kernel/transpose/cpu.hh>
 
 namespace nk = nntile::kernel;
 using nntile::fp32_t;
@@ -83,6 +86,31 @@ extern "C" void ref_accumulate_attn_output_##suffix(i64 head, i64 seq, \
 
 REF_TYPED(f32, fp32_t)
 REF_TYPED(bf16, bf16_t)
+
+// The layout / rotation / bias kernels around the SDPA layer.
+#define REF_AROUND(suffix, TYPE) \
+extern "C" void ref_transpose_##suffix(i64 m, i64 n, float alpha, \
+        const void *src, void *dst) \
+{ \
+    nk::transpose::cpu<TYPE>(m, n, alpha, static_cast<const TYPE *>(src), \
+            static_cast<TYPE *>(dst)); \
+} \
+extern "C" void ref_rope_##suffix(i64 m, i64 n, const void *sn, \
+        const void *cs, const void *src, void *dst) \
+{ \
+    nk::rope::cpu<TYPE>(m, n, static_cast<const TYPE *>(sn), \
+            static_cast<const TYPE *>(cs), static_cast<const TYPE *>(src), \
+            static_cast<TYPE *>(dst)); \
+} \
+extern "C" void ref_add_fiber_inplace_##suffix(i64 m, i64 n, i64 k, \
+        i64 batch, float alpha, const void *src, float beta, void *dst) \
+{ \
+    nk::add_fiber_inplace::cpu<TYPE>(m, n, k, batch, alpha, \
+            static_cast<const TYPE *>(src), beta, static_cast<TYPE *>(dst)); \
+}
+
+REF_AROUND(f32, fp32_t)
+REF_AROUND(bf16, bf16_t)
 
 // Batched column-major sgemm exactly as the reference's CPU codelet calls it.
 extern "C" void ref_gemm_f32(int transA, int transB, i64 m, i64 n,

@@ -11,6 +11,13 @@ if ROOT not in sys.path:
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
+def reference_root():
+    """The reference checkout when there is one here: $NNTILE_REFERENCE_ROOT, else a
+    directory named ``reference`` beside the repository.  None on a GPU box."""
+    from oracle import build as oracle_build
+    return oracle_build.default_ref_root()
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
 

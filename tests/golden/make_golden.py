@@ -175,11 +175,34 @@ def flash_vectors():
     return out
 
 
+def around_vectors():
+    """The passes the reference's attention layers run around the SDPA layer
+    (transpose + rope, transpose + bias, transpose back), by its own CPU kernels."""
+    assert O.have_ref(), "build oracle/_ref first (needs the reference checkout)"
+    rng = np.random.default_rng(77)
+    out = {}
+    for tag, (lead, head, seq, batch) in {"llama_q": (8, 64, 7, 3), "llama_k": (2, 128, 5, 2),
+                                           "gpt2": (12, 64, 6, 2)}.items():
+        proj = O.to_bf16(np.asfortranarray(
+            rng.standard_normal((lead, head, seq, batch)).astype(np.float32)))
+        pos = np.tile(np.arange(seq) + 3, (batch, 1))
+        sin, cos = (O.to_bf16(x) for x in O.rope_sin_cos(head, pos))
+        bias = O.to_bf16(np.asfortranarray(rng.standard_normal((head, lead)).astype(np.float32)))
+        out[f"{tag}_proj"], out[f"{tag}_sin"], out[f"{tag}_cos"] = proj, sin, cos
+        out[f"{tag}_bias"] = bias
+        out[f"{tag}_rope"] = O.attention_prologue(proj, sin, cos, backend="ref")
+        out[f"{tag}_plain"] = O.attention_prologue(proj, backend="ref")
+        out[f"{tag}_biased"] = O.attention_prologue(proj, bias=bias, backend="ref")
+        out[f"{tag}_back"] = O.attention_epilogue(out[f"{tag}_rope"], backend="ref")
+    return out
+
+
 def main():
+    np.savez_compressed(os.path.join(HERE, "ref_around.npz"), **around_vectors())
     np.savez_compressed(os.path.join(HERE, "ref_kernels.npz"), **ref_kernel_vectors())
     np.savez_compressed(os.path.join(HERE, "ref_chain.npz"), **chain_vectors())
     np.savez_compressed(os.path.join(HERE, "flash_preset.npz"), **flash_vectors())
-    for f in ("ref_kernels.npz", "ref_chain.npz", "flash_preset.npz"):
+    for f in ("ref_kernels.npz", "ref_chain.npz", "flash_preset.npz", "ref_around.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

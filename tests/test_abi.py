@@ -26,7 +26,7 @@ def declared_symbols():
 
 def test_every_declared_symbol_is_exported(lib):
     names = declared_symbols()
-    assert len(names) >= 29
+    assert len(names) >= 40
     for n in names:
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
     # and the Python binding knows the signature of each of them
@@ -85,3 +85,40 @@ def test_cpp_shims_compile_and_reach_the_library(lib, tmp_path):
                     os.path.join(ROOT, "tests", "shim_check.cc"), _lib.LIB_PATH,
                     "-Wl,-rpath," + libdir], check=True)
     assert subprocess.run([exe]).returncode == 0
+
+
+def test_per_device_bookkeeping(tmp_path):
+    """The shared-memory opt-in of the fused kernels, the helper streams and the
+    no-allocation scratch address are set up once PER DEVICE (one process may drive
+    several GPUs); the bookkeeping class is plain C++ and is checked here."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    exe = str(tmp_path / "per_device_check")
+    subprocess.run(["g++", "-std=c++17", "-o", exe,
+                    os.path.join(ROOT, "tests", "per_device_check.cc")], check=True)
+    assert subprocess.run([exe]).returncode == 0
+
+
+def test_new_entry_points_check_their_arguments(lib):
+    null = ctypes.c_void_p(0)
+    # GEMM: null handle / buffers, negative size
+    assert lib.nntile_b200_gemm_fp32(null, 1, 0, 4, 4, 4, 1, 1.0, null, null, 0.0, null) == -1
+    assert lib.nntile_b200_gemm_bf16(null, 0, 0, -1, 4, 4, 1, 1.0, null, null, 0.0, null) == -1
+    assert lib.nntile_b200_gemm_bf16(null, 0, 0, 0, 4, 4, 1, 1.0, null, null, 0.0, null) == 0
+    # layout changes: odd lead / head are rejected, empty problems are fine
+    assert lib.nntile_b200_transpose_rope_bf16(null, 7, 64, 4, 1, null, null, null, null) == -2
+    assert lib.nntile_b200_transpose_rope_bf16(null, 8, 64, 0, 1, null, null, null, null) == 0
+    assert lib.nntile_b200_transpose_rope_bf16(null, 8, 64, 4, 1, null, null, null, null) == -1
+    assert lib.nntile_b200_transpose_bias_bf16(null, 12, 64, 4, 1, null, null, null) == -1
+    assert lib.nntile_b200_transpose_heads_back_bf16(null, 12, 63, 4, 1, null, null) == -2
+    # status reader
+    assert lib.nntile_b200_flash_sdpa_read_status(null, null, None) == -1
+    # tensor level: scratch size grows with the tensor, not only with the tile
+    i64 = ctypes.c_int64
+    base = (i64*5)(128, 2048, 1, 1, 16)
+    small = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes((i64*5)(128, 2048, 1, 1, 16), base)
+    big = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes((i64*5)(128, 16384, 1, 1, 16), base)
+    assert 0 < small < big
+    assert lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(None, base) == 0

@@ -313,7 +313,7 @@ def test_null_mask_tile_skips_the_pair():
     mi = dev(O.to_bf16(F(np.full((St, St), -np.inf, np.float32))))
     i64 = ctypes.c_int64
     shape, base = (i64*5)(D, S, 1, 1, H), (i64*5)(D, St, 1, 1, H)
-    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(base)
+    nbytes = lib.nntile_b200_tensor_flash_sdpa_scratch_bytes(shape, base)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     parr = lambda ps: ctypes.cast((ctypes.c_void_p*len(ps))(*ps), ctypes.POINTER(ctypes.c_void_p))
     ptrs = lambda ts: parr([t.data_ptr() for t in ts])
@@ -334,8 +334,16 @@ def test_null_mask_tile_skips_the_pair():
         assert st == 0
         torch.cuda.synchronize()
         results.append([torch.stack(x) for x in (A, lse, dQ, dK, dV)])
-    for full, skipped in zip(*results):
-        assert torch.equal(full, skipped)       # a fully masked task changes nothing
+    names = ("A", "lse", "dQ", "dK", "dV")
+    for name, full, skipped in zip(names, *results):
+        if name == "dQ":
+            # dQ of a Q tile is summed in fp32 by red.add in whatever order the CTAs
+            # finish; the sums agree to fp32 rounding, i.e. to one bf16 step at most
+            d = (full.float() - skipped.float()).abs()
+            assert float((d/(full.float().abs() + 1e-3)).max()) <= 2.0**-7
+            assert float((d > 0).float().mean()) <= 1e-3
+        else:
+            assert torch.equal(full, skipped)   # a fully masked task changes nothing
 
 
 def test_layer_forward_dynamic_prefill_then_decode():

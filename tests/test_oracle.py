@@ -216,3 +216,19 @@ def test_kv_cache_append_restatement():
     assert np.array_equal(cache, np.concatenate(parts, axis=1))
     with pytest.raises(ValueError):
         O.kv_cache_append(cache, n, parts[1])
+
+
+@pytest.mark.parametrize("tag", ["llama_q", "llama_k", "gpt2"])
+def test_prologue_restatement_matches_reference_kernels(golden, tag):
+    """transpose + rope, transpose + bias and the transposition back, restated in C,
+    against the outputs of the reference's own transpose / rope / add_fiber_inplace
+    CPU kernels (tests/golden/ref_around.npz): bit for bit."""
+    g = golden("ref_around.npz")
+    proj, sin, cos, bias = (g[f"{tag}_{k}"] for k in ("proj", "sin", "cos", "bias"))
+    assert np.array_equal(O.attention_prologue(proj, sin, cos), g[f"{tag}_rope"])
+    assert np.array_equal(O.attention_prologue(proj), g[f"{tag}_plain"])
+    assert np.array_equal(O.attention_prologue(proj, bias=bias), g[f"{tag}_biased"])
+    assert np.array_equal(O.attention_epilogue(g[f"{tag}_rope"]), g[f"{tag}_back"])
+    if O.have_ref():
+        assert np.array_equal(O.attention_prologue(proj, sin, cos, backend="ref"),
+                              g[f"{tag}_rope"])
