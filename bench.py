@@ -351,11 +351,15 @@ class FlashWorkload:
                            v(self.dk), v(self.dq), v(self.dv))
 
 
-def time_steps(torch, fn, steps, warmup, barrier=None, split=None):
+def time_steps(torch, fn, steps, warmup, barrier=None, split=None, finish=None):
     """CUDA-event timing of `steps` calls on the current stream.  `split` is an
-    optional pair of callables (fwd, bwd) timed separately inside each step."""
+    optional pair of callables (fwd, bwd) timed separately inside each step;
+    `finish` is called after the last step, inside the timed region (a pipeline
+    that runs on other streams joins the current one there)."""
     for _ in range(warmup):
         fn()
+    if finish:
+        finish()
     torch.cuda.synchronize()
     if barrier:
         barrier()
@@ -374,6 +378,8 @@ def time_steps(torch, fn, steps, warmup, barrier=None, split=None):
             marks.append((a, b, c))
         else:
             fn()
+    if finish:
+        finish()
     stop.record()
     torch.cuda.synchronize()
     if barrier:
@@ -414,6 +420,20 @@ def run_gpu_arm(args):
         res = run_decode(torch, ops, dev, peaks, c5, max(args.steps, 1), args.warmup)
         if rank == 0:
             print(json.dumps({"profile_run": True, "workload": args.workload, **res}), flush=True)
+        return
+    if args.workload == "c2":
+        # config 2 only, for profiler captures of the head-64 kernels
+        wl = FlashWorkload(C2, dev, seed=1, rope=False)
+        ms, _, _ = time_steps(torch, wl.step, max(args.steps, 1), args.warmup)
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": "c2",
+                              "ms_per_step": ms/max(args.steps, 1)}), flush=True)
+        return
+    if args.workload == "hbm":
+        # the HBM-bound kernels only (layout changes, unfused chain), for profiler captures
+        res = run_hbm_kernels(torch, ops, dev, peaks, max(args.steps, 1))
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": "hbm", **res}), flush=True)
         return
     from nntile_b200.parallel import shard_range
     full_cfg = C3 if args.workload == "c3" else C3_SMALL
@@ -495,7 +515,7 @@ def run_gpu_arm(args):
                               "roofline": roofline}), flush=True)
         return
     # ---- e2e: host buffers, copies inside the timed region --------------------
-    e2e_steps = max(1, min(args.steps, 5))
+    e2e_steps = max(1, min(args.steps, 8))
     host_in = [x.cpu().pin_memory() for x in (wl.q, wl.k, wl.v, wl.dy)]
     host_out = [torch.empty_like(x, device="cpu").pin_memory()
                 for x in (wl.y, wl.dq, wl.dk, wl.dv)]
@@ -508,10 +528,11 @@ def run_gpu_arm(args):
     dev_in, dev_out = [wl.by_unit(x) for x in dev_in], [wl.by_unit(x) for x in dev_out]
 
     def e2e_step():
-        # copies of one chunk of units overlap the kernels of the previous one
+        # copies of one chunk of units overlap the kernels of the previous one, and
+        # the copy-in of the next step overlaps the copy-out of this one
         pipe.step(host_in, dev_in, wl.step_units, dev_out, host_out)
 
-    e2e_ms, _, _ = time_steps(torch, e2e_step, e2e_steps, 1, barrier)
+    e2e_ms, _, _ = time_steps(torch, e2e_step, e2e_steps, 1, barrier, finish=pipe.join)
     t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -803,7 +824,7 @@ def run_e2e_gqa(torch, ops, dev, cfg, flops_step, steps):
     host_out = [torch.empty_like(x, device="cpu").pin_memory() for x in (y, dq, dk, dv)]
     pipe = HostStream(dev, H, chunks=H)
     step = lambda: pipe.step(host_in, (q, k, v, dy), body, (y, dq, dk, dv), host_out)
-    ms, _, _ = time_steps(torch, step, steps, 1)
+    ms, _, _ = time_steps(torch, step, steps, 1, finish=pipe.join)
     ms /= steps
     return {"value": flops_step/(ms*1e-3)/1e12, "unit": UNIT, "ms_per_step": ms,
             "h2d_bytes_per_step": sum(x.numel()*x.element_size() for x in host_in),
@@ -973,9 +994,12 @@ def main(argv=None):
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--workload", choices=["c3", "small", "decode", "decode-small"], default="c3",
-                    help="c3 = BASELINE config 3 per GPU (the headline); small = the same "
-                         "kernels on 16 slices, for profiler captures")
+    ap.add_argument("--workload", choices=["c3", "small", "decode", "decode-small", "c2", "hbm"],
+                    default="c3",
+                    help="c3 = BASELINE config 3 (the headline); the others are profiler-capture "
+                         "runs: small = the same kernels on 16 slices, decode / decode-small = "
+                         "config 5 (a quarter of its batch), c2 = config 2 (head 64), hbm = the "
+                         "HBM-bound kernels around the fused pair")
     ap.add_argument("--profile", action="store_true",
                     help="run only the timed forward/backward steps (no e2e, extras or CPU "
                          "baseline) and print a short line; for use under a profiler")

@@ -17,7 +17,148 @@ namespace nb200 {
 
 std::atomic<unsigned long long> g_kernel_launches{0};
 
+// ------------------------------------------------------- 16-byte vector access
+// The hot shapes of the chain (m == 1: fibres are contiguous; whole tensors for the
+// elementwise ops) are walked in 16-byte pieces - 8 bf16 or 4 fp32 values per
+// thread and access - whenever the fibre length and the pointers allow it; the
+// scalar kernels below cover everything else.
+template<typename T> struct Vec;
+template<> struct Vec<float> { static constexpr int N = 4; };
+template<> struct Vec<bf16> { static constexpr int N = 8; };
+
+__device__ __forceinline__ void vload(const float *p, float (&v)[4])
+{
+    const float4 x = *reinterpret_cast<const float4 *>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+
+__device__ __forceinline__ void vload(const bf16 *p, float (&v)[8])
+{
+    const uint4 x = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for(int e = 0; e < 4; ++e)
+    {
+        v[2*e] = __uint_as_float(w[e] << 16);
+        v[2*e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+    }
+}
+
+__device__ __forceinline__ void vstore(float *p, const float (&v)[4])
+{
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+__device__ __forceinline__ void vstore(bf16 *p, const float (&v)[8])
+{
+    uint32_t w[4];
+#pragma unroll
+    for(int e = 0; e < 4; ++e)
+    {
+        w[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v[2*e]))
+                | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v[2*e + 1])) << 16);
+    }
+    *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// exp for the vector kernels: the accurate expf for fp32 storage (the chain's 1e-5
+// bar), the two-instruction ex2-based form for bf16 storage, whose own rounding
+// (2^-9) is four orders of magnitude coarser than that form's error.
+__device__ __forceinline__ float exp_for(const float *, float x) { return expf(x); }
+__device__ __forceinline__ float exp_for(const bf16 *, float x) { return __expf(x); }
+
+template<typename T>
+inline bool vec_ok(Index fibre_len, const void *a, const void *b = nullptr, const void *c = nullptr)
+{
+    return fibre_len % Vec<T>::N == 0 && aligned16(a) && (!b || aligned16(b)) && (!c || aligned16(c));
+}
+
+// Lanes that share one fibre of `k` elements: the smallest power of two that gives
+// every lane at least one 16-byte piece, at most a warp.
+template<typename T>
+inline int lanes_per_fibre(Index k)
+{
+    const Index pieces = k/Vec<T>::N;
+    int l = 1;
+    while(l < 32 && l < pieces) l <<= 1;
+    return l;
+}
+
+// Blocks of 256 threads for `n` fibres at `lpf` lanes each: enough to fill the 148
+// SMs eight blocks deep, never more than the fibres need.
+inline unsigned fibre_grid(Index n, int lpf)
+{
+    const Index per_block = 256/lpf;
+    Index blocks = (n + per_block - 1)/per_block;
+    if(blocks > 148*8) blocks = 148*8;
+    return (unsigned)(blocks < 1 ? 1 : blocks);
+}
+
 // ---------------------------------------------------------------- mask_scalar
+// Vector form: grid.y walks the columns, threads walk the 16-byte pieces of a
+// column.  A piece whose mask bytes are all "keep" is not touched at all, one whose
+// bytes are all "drop" is written without being read.
+template<typename T>
+__global__ void __launch_bounds__(256)
+mask_scalar_vec_kernel(Index nrows, Index ncols, const uint8_t *__restrict__ mask, float val,
+        T *__restrict__ data)
+{
+    constexpr int N = Vec<T>::N;
+    const Index pieces = nrows/N;
+    for(Index col = blockIdx.y; col < ncols; col += gridDim.y)
+    {
+        T *column = data + col*nrows;
+        for(Index v = (Index)blockIdx.x*blockDim.x + threadIdx.x; v < pieces;
+                v += (Index)gridDim.x*blockDim.x)
+        {
+            uint8_t keep[N];
+            if(N == 8)
+            {
+                const uint2 m = *reinterpret_cast<const uint2 *>(mask + v*N);
+#pragma unroll
+                for(int e = 0; e < 4; ++e)
+                {
+                    keep[e] = (uint8_t)(m.x >> (8*e));
+                    keep[4 + e] = (uint8_t)(m.y >> (8*e));
+                }
+            }
+            else
+            {
+                const uint32_t m = *reinterpret_cast<const uint32_t *>(mask + v*N);
+#pragma unroll
+                for(int e = 0; e < N; ++e)
+                {
+                    keep[e] = (uint8_t)(m >> (8*e));
+                }
+            }
+            bool all_keep = true, all_drop = true;
+#pragma unroll
+            for(int e = 0; e < N; ++e)
+            {
+                all_keep &= keep[e] != 0;
+                all_drop &= keep[e] == 0;
+            }
+            if(all_keep)
+            {
+                continue;
+            }
+            float x[N];
+            if(all_drop)
+            {
+#pragma unroll
+                for(int e = 0; e < N; ++e) x[e] = val;
+            }
+            else
+            {
+                vload(column + v*N, x);
+#pragma unroll
+                for(int e = 0; e < N; ++e) x[e] = keep[e] ? x[e] : val;
+            }
+            vstore(column + v*N, x);
+        }
+    }
+}
+
 template<typename T>
 __global__ void mask_scalar_kernel(Index nrows, Index total, const uint8_t *mask,
         float val, T *data)
@@ -123,6 +264,69 @@ __global__ void maxsumexp_m1_kernel(Index n, Index k, const T *src, T *dst)
     }
 }
 
+// m == 1, vector form: `lpf` lanes share a fibre and walk it in 16-byte pieces.  Per
+// piece: the maximum of its finite values, one rescale of the running sum when the
+// maximum grows, then one exponential per value (exp(-inf) = 0 drops masked ones).
+template<typename T>
+__global__ void __launch_bounds__(256)
+maxsumexp_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ src, T *dst)
+{
+    constexpr int N = Vec<T>::N;
+    const int sub = threadIdx.x & (lpf - 1);
+    const Index groups = ((Index)gridDim.x*blockDim.x)/lpf;
+    for(Index j = ((Index)blockIdx.x*blockDim.x + threadIdx.x)/lpf; j < n; j += groups)
+    {
+        const T *fib = src + j*k;
+        MaxSum acc = {-CUDART_INF_F, 0.0f};
+        bool poisoned = false;
+        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        {
+            float x[N];
+            vload(fib + l, x);
+            if(l == 0)
+            {
+                // a leading +inf makes the reference give up on the fibre
+                poisoned = isinf(x[0]) && x[0] > 0.0f;
+            }
+            float top = -CUDART_INF_F;
+#pragma unroll
+            for(int e = 0; e < N; ++e)
+            {
+                x[e] = isinf(x[e]) ? -CUDART_INF_F : x[e];     // +inf is skipped like -inf
+                top = fmaxf(top, x[e]);
+            }
+            if(top == -CUDART_INF_F)
+            {
+                continue;
+            }
+            if(top > acc.top)
+            {
+                acc.sum *= exp_for(fib, acc.top - top);        // exp(-inf) = 0: empty pair
+                acc.top = top;
+            }
+            float part = 0.0f;
+#pragma unroll
+            for(int e = 0; e < N; ++e)
+            {
+                part += exp_for(fib, x[e] - acc.top);
+            }
+            acc.sum += part;
+        }
+        for(int o = lpf >> 1; o > 0; o >>= 1)
+        {
+            MaxSum other;
+            other.top = __shfl_xor_sync(0xffffffffu, acc.top, o);
+            other.sum = __shfl_xor_sync(0xffffffffu, acc.sum, o);
+            acc = ms_join(acc, other);
+        }
+        poisoned = __shfl_sync(0xffffffffu, (int)poisoned, (threadIdx.x & 31) & ~(lpf - 1)) != 0;
+        if(sub == 0 && !poisoned)
+        {
+            ms_store(acc, dst + 2*j);
+        }
+    }
+}
+
 // General m: one thread per (i, j); neighbouring threads read neighbouring i.
 template<typename T>
 __global__ void maxsumexp_kernel(Index m, Index n, Index k, const T *src, T *dst)
@@ -161,7 +365,68 @@ __global__ void softmax_inplace_kernel(Index m, Index k, Index total, const T *m
     }
 }
 
+// m == 1, vector form: the (max, sum) pair and alpha/sum are read and formed once per
+// fibre, each value costs one exponential and one product.
+template<typename T>
+__global__ void __launch_bounds__(256)
+softmax_inplace_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ mse, float alpha,
+        T *dst)
+{
+    constexpr int N = Vec<T>::N;
+    const int sub = threadIdx.x & (lpf - 1);
+    const Index groups = ((Index)gridDim.x*blockDim.x)/lpf;
+    for(Index j = ((Index)blockIdx.x*blockDim.x + threadIdx.x)/lpf; j < n; j += groups)
+    {
+        const float top = ld(mse[2*j]), scale = alpha/ld(mse[2*j + 1]);
+        T *fib = dst + j*k;
+        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        {
+            float x[N];
+            vload(fib + l, x);
+#pragma unroll
+            for(int e = 0; e < N; ++e)
+            {
+                x[e] = isinf(x[e]) ? 0.0f : exp_for(fib, x[e] - top)*scale;
+            }
+            vstore(fib + l, x);
+        }
+    }
+}
+
 // -------------------------------------------------------------- sumprod_slice
+template<typename T>
+__global__ void __launch_bounds__(256)
+sumprod_slice_m1_vec_kernel(Index n, Index k, int lpf, float alpha, const T *__restrict__ a,
+        const T *__restrict__ b, float beta, T *dst)
+{
+    constexpr int N = Vec<T>::N;
+    const int sub = threadIdx.x & (lpf - 1);
+    const Index groups = ((Index)gridDim.x*blockDim.x)/lpf;
+    for(Index j = ((Index)blockIdx.x*blockDim.x + threadIdx.x)/lpf; j < n; j += groups)
+    {
+        float acc = 0.0f;
+        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        {
+            float x[N], y[N];
+            vload(a + j*k + l, x);
+            vload(b + j*k + l, y);
+#pragma unroll
+            for(int e = 0; e < N; ++e)
+            {
+                acc = fmaf(x[e], y[e], acc);
+            }
+        }
+        for(int o = lpf >> 1; o > 0; o >>= 1)
+        {
+            acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        }
+        if(sub == 0)
+        {
+            st(dst[j], beta == 0.0f ? alpha*acc : beta*ld(dst[j]) + alpha*acc);
+        }
+    }
+}
+
 template<typename T>
 __global__ void sumprod_slice_m1_kernel(Index n, Index k, float alpha, const T *a,
         const T *b, float beta, T *dst)
@@ -211,6 +476,54 @@ __global__ void add_slice_inplace_kernel(Index m, Index k, Index total, float al
     {
         const Index i = x % m, j = x/mk;
         st(dst[x], beta*ld(dst[x]) + alpha*ld(src[j*m + i]));
+    }
+}
+
+// m == 1, vector form: one slice value per fibre.
+template<typename T>
+__global__ void __launch_bounds__(256)
+add_slice_inplace_m1_vec_kernel(Index n, Index k, int lpf, float alpha, const T *__restrict__ src,
+        float beta, T *dst)
+{
+    constexpr int N = Vec<T>::N;
+    const int sub = threadIdx.x & (lpf - 1);
+    const Index groups = ((Index)gridDim.x*blockDim.x)/lpf;
+    for(Index j = ((Index)blockIdx.x*blockDim.x + threadIdx.x)/lpf; j < n; j += groups)
+    {
+        const float add = alpha*ld(src[j]);
+        T *fib = dst + j*k;
+        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        {
+            float x[N];
+            vload(fib + l, x);
+#pragma unroll
+            for(int e = 0; e < N; ++e)
+            {
+                x[e] = beta*x[e] + add;
+            }
+            vstore(fib + l, x);
+        }
+    }
+}
+
+// dst = alpha*src*dst (MUL) or alpha*src + beta*dst (ADD), 16 bytes per thread.
+template<typename T, bool MUL>
+__global__ void __launch_bounds__(256)
+binary_inplace_vec_kernel(Index pieces, float alpha, const T *__restrict__ src, float beta, T *dst)
+{
+    constexpr int N = Vec<T>::N;
+    const Index stride = (Index)gridDim.x*blockDim.x;
+    for(Index v = (Index)blockIdx.x*blockDim.x + threadIdx.x; v < pieces; v += stride)
+    {
+        float x[N], y[N];
+        vload(src + v*N, x);
+        vload(dst + v*N, y);
+#pragma unroll
+        for(int e = 0; e < N; ++e)
+        {
+            y[e] = MUL ? alpha*y[e]*x[e] : alpha*x[e] + beta*y[e];
+        }
+        vstore(dst + v*N, y);
     }
 }
 
@@ -298,6 +611,17 @@ int mask_scalar_run(cudaStream_t s, Index nrows, Index ncols, const uint8_t *mas
     if(nrows == 0 || ncols == 0) return NNTILE_B200_OK;
     if(!mask || !data) return NNTILE_B200_E_BADARG;
     const Index total = nrows*ncols;
+    if(vec_ok<T>(nrows, data) && (reinterpret_cast<uintptr_t>(mask) & 7u) == 0)
+    {
+        const Index pieces = nrows/Vec<T>::N;
+        Index gx = (pieces + 255)/256, gy = ncols;
+        if(gx > 148*4) gx = 148*4;
+        if(gy > 1024) gy = 1024;
+        while(gx*gy > 148*32 && gy > 1) gy = (gy + 1)/2;
+        mask_scalar_vec_kernel<T><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(nrows, ncols,
+                mask, val, data);
+        return launch_status();
+    }
     mask_scalar_kernel<T><<<grid_for(total, 256), 256, 0, s>>>(nrows, total, mask, val, data);
     return launch_status();
 }
@@ -308,7 +632,12 @@ int maxsumexp_run(cudaStream_t s, Index m, Index n, Index k, const T *src, T *ds
     if(m < 0 || n < 0 || k < 0) return NNTILE_B200_E_BADARG;
     if(m == 0 || n == 0 || k == 0) return NNTILE_B200_OK;
     if(!src || !dst) return NNTILE_B200_E_BADARG;
-    if(m == 1)
+    if(m == 1 && vec_ok<T>(k, src))
+    {
+        const int lpf = lanes_per_fibre<T>(k);
+        maxsumexp_m1_vec_kernel<T><<<fibre_grid(n, lpf), 256, 0, s>>>(n, k, lpf, src, dst);
+    }
+    else if(m == 1)
     {
         // 8 warps per block, one fibre per warp per pass
         Index blocks = (n + 7)/8;
@@ -330,6 +659,13 @@ int softmax_inplace_run(cudaStream_t s, Index m, Index n, Index k, const T *mse,
     if(m == 0 || n == 0 || k == 0) return NNTILE_B200_OK;
     if(!mse || !dst) return NNTILE_B200_E_BADARG;
     const Index total = m*n*k;
+    if(m == 1 && vec_ok<T>(k, dst))
+    {
+        const int lpf = lanes_per_fibre<T>(k);
+        softmax_inplace_m1_vec_kernel<T><<<fibre_grid(n, lpf), 256, 0, s>>>(n, k, lpf, mse, alpha,
+                dst);
+        return launch_status();
+    }
     softmax_inplace_kernel<T><<<grid_for(total, 256), 256, 0, s>>>(m, k, total, mse, alpha, dst);
     return launch_status();
 }
@@ -341,7 +677,13 @@ int sumprod_slice_run(cudaStream_t s, Index m, Index n, Index k, float alpha,
     if(m < 0 || n < 0 || k < 0) return NNTILE_B200_E_BADARG;
     if(m == 0 || n == 0) return NNTILE_B200_OK;
     if(!dst || (k > 0 && (!a || !b))) return NNTILE_B200_E_BADARG;
-    if(m == 1)
+    if(m == 1 && k > 0 && vec_ok<T>(k, a, b))
+    {
+        const int lpf = lanes_per_fibre<T>(k);
+        sumprod_slice_m1_vec_kernel<T><<<fibre_grid(n, lpf), 256, 0, s>>>(n, k, lpf, alpha, a, b,
+                beta, dst);
+    }
+    else if(m == 1)
     {
         Index blocks = (n + 7)/8;
         if(blocks > 148*8) blocks = 148*8;
@@ -362,6 +704,13 @@ int add_slice_inplace_run(cudaStream_t s, Index m, Index n, Index k, float alpha
     if(m == 0 || n == 0 || k == 0) return NNTILE_B200_OK;
     if(!src || !dst) return NNTILE_B200_E_BADARG;
     const Index total = m*n*k;
+    if(m == 1 && vec_ok<T>(k, dst))
+    {
+        const int lpf = lanes_per_fibre<T>(k);
+        add_slice_inplace_m1_vec_kernel<T><<<fibre_grid(n, lpf), 256, 0, s>>>(n, k, lpf, alpha, src,
+                beta, dst);
+        return launch_status();
+    }
     add_slice_inplace_kernel<T><<<grid_for(total, 256), 256, 0, s>>>(m, k, total, alpha, src, beta, dst);
     return launch_status();
 }
@@ -372,6 +721,13 @@ int multiply_inplace_run(cudaStream_t s, Index nelems, float alpha, const T *src
     if(nelems < 0) return NNTILE_B200_E_BADARG;
     if(nelems == 0) return NNTILE_B200_OK;
     if(!src || !dst) return NNTILE_B200_E_BADARG;
+    if(vec_ok<T>(nelems, src, dst))
+    {
+        const Index pieces = nelems/Vec<T>::N;
+        binary_inplace_vec_kernel<T, true><<<grid_for(pieces, 256, 2), 256, 0, s>>>(pieces, alpha,
+                src, 0.0f, dst);
+        return launch_status();
+    }
     multiply_inplace_kernel<T><<<grid_for(nelems, 256), 256, 0, s>>>(nelems, alpha, src, dst);
     return launch_status();
 }
@@ -383,6 +739,13 @@ int add_inplace_run(cudaStream_t s, Index nelems, float alpha, const T *src, flo
     if(nelems < 0) return NNTILE_B200_E_BADARG;
     if(nelems == 0) return NNTILE_B200_OK;
     if(!src || !dst) return NNTILE_B200_E_BADARG;
+    if(vec_ok<T>(nelems, src, dst))
+    {
+        const Index pieces = nelems/Vec<T>::N;
+        binary_inplace_vec_kernel<T, false><<<grid_for(pieces, 256, 2), 256, 0, s>>>(pieces, alpha,
+                src, beta, dst);
+        return launch_status();
+    }
     add_inplace_kernel<T><<<grid_for(nelems, 256), 256, 0, s>>>(nelems, alpha, src, beta, dst);
     return launch_status();
 }

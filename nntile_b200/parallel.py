@@ -65,16 +65,19 @@ def chunk_ranges(n_units: int, chunks: int) -> list[tuple[int, int]]:
 
 class HostStream:
     """Runs a per-unit body on tensors that live in pinned host memory, with the
-    copies overlapped with the kernels.
+    copies overlapped with the kernels - inside a step and from one step to the next.
 
     The reference leaves this to StarPU: its codelets are STARPU_CUDA_ASYNC
     (src/starpu/codelet.cc:80), so the runtime moves the next task's handles to the
     GPU and the previous task's results back while a task computes.  Here the
-    leading (kv head) index of the buffers is cut into chunks - every kv head is an
-    independent problem - and three streams are chained by events: host-to-device
-    copy of chunk c+1, kernels of chunk c, device-to-host copy of chunk c-1.  PCIe
-    is full duplex, so a step costs about max(copy in, copy out) instead of
-    copy in + kernels + copy out.
+    leading index of the buffers (independent units) is cut into chunks and three
+    streams are chained by events, chunk by chunk: host-to-device copy of a chunk,
+    its kernels, device-to-host copy of its results.  Nothing waits for a whole
+    step: the copy-in of chunk c of step k+1 only waits for the kernels of chunk c
+    of step k (which read the same device buffers), and those kernels only wait for
+    the copy-out of chunk c of step k.  PCIe is full duplex, so a stream of steps
+    costs about max(copy in, copy out) per step instead of copy in + kernels +
+    copy out.  `join()` makes the current stream wait for the last results.
 
     `body(lo, hi)` enqueues the kernels for units [lo, hi) on the current stream;
     all tensors are indexed by unit along axis 0."""
@@ -86,23 +89,39 @@ class HostStream:
         self.s_out = torch.cuda.Stream(device=device)
         self.ev_in = [torch.cuda.Event() for _ in self.ranges]
         self.ev_done = [torch.cuda.Event() for _ in self.ranges]
+        self.ev_out = [torch.cuda.Event() for _ in self.ranges]
+        self.started = False
 
     def step(self, host_in, dev_in, body, dev_out, host_out):
         cur = torch.cuda.current_stream(self.device)
-        # the previous step's kernels must be done with the device buffers
-        self.s_in.wait_stream(cur)
+        if not self.started:
+            # whatever filled or still reads the device buffers comes first
+            self.s_in.wait_stream(cur)
+            self.s_out.wait_stream(cur)
         for c, (lo, hi) in enumerate(self.ranges):
+            if self.started:
+                self.s_in.wait_event(self.ev_done[c])     # last step's kernels read dev_in[c]
             with torch.cuda.stream(self.s_in):
                 for h, d in zip(host_in, dev_in):
                     d[lo:hi].copy_(h[lo:hi], non_blocking=True)
                 self.ev_in[c].record(self.s_in)
         for c, (lo, hi) in enumerate(self.ranges):
             cur.wait_event(self.ev_in[c])
+            if self.started:
+                cur.wait_event(self.ev_out[c])            # last step's results have left dev_out[c]
             body(lo, hi)
             self.ev_done[c].record(cur)
             self.s_out.wait_event(self.ev_done[c])
             with torch.cuda.stream(self.s_out):
                 for h, d in zip(host_out, dev_out):
                     h[lo:hi].copy_(d[lo:hi], non_blocking=True)
-        # the step is over when its last result is on the host
+                self.ev_out[c].record(self.s_out)
+        self.started = True
+
+    def join(self):
+        """The current stream waits until every result enqueued so far is on the host
+        (and every copy-in is done); the next step() starts a fresh pipeline."""
+        cur = torch.cuda.current_stream(self.device)
         cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_in)
+        self.started = False
