@@ -402,11 +402,19 @@ def run_gpu_arm(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback "
                          "(use --impl reference for the CPU arm)")
+    ngpu = torch.cuda.device_count()
+    oversubscribed = world > ngpu
+    local = local % ngpu
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        if oversubscribed:
+            # more ranks than GPUs: a functional run only (NCCL wants one GPU per rank);
+            # the ranks share devices and talk over gloo, and the line says so
+            dist.init_process_group("gloo")
+        else:
+            dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
     peaks = measured_peaks()
 
@@ -587,7 +595,9 @@ def run_gpu_arm(args):
                 "l2": ("inputs_exceed_l2 (Q,K,V,dY,A %d MB each per GPU vs 126 MB L2)"
                        % (cfg["kv_heads"]*cfg["group"]*cfg["batch"]*cfg["seq"]*cfg["head"]*2 >> 20)),
                 "parallelism": f"{world} shards of {cfg['kv_heads']*cfg['batch']} (batch, kv head) "
-                               "units each, no collective",
+                               "units each, no collective"
+                               + (f"; FUNCTIONAL RUN ONLY: {world} ranks share {ngpu} GPU(s)"
+                                  if oversubscribed else ""),
                 "paths": {"fwd": fwd_path, "bwd": bwd_path,
                           "legend": "2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel"},
             },

@@ -246,7 +246,7 @@ int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_t batch);
  *   dst[2i, .., n]   = cos[i,..]*x[2i] - sin[i,..]*x[2i+1]
  *   dst[2i+1, .., n] = sin[i,..]*x[2i] + cos[i,..]*x[2i+1],  x = src[n, :, ..]
  * fp32 arithmetic without fused multiply-add, one rounding to bf16: bit-identical to
- * the two reference passes.  lead and head even, pointers 16-byte aligned.
+ * the two reference passes.  lead even, head a multiple of 8, pointers 16-byte aligned.
  * Replaces transpose_async(1.0, src, tmp, ndim) followed by rope_async(sin, cos, tmp,
  * dst) (wrappers/python/nntile/model/llama_attention.py:592-625; kernels
  * nntile::kernel::transpose::cuda<T>, src/kernel/transpose/cuda.cu:24-132, and

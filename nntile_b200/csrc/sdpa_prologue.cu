@@ -18,9 +18,12 @@
 // One CTA handles `tp` consecutive (seq, batch) positions at a time: their
 // lead*head*tp source elements are one contiguous run, and for every value of
 // `lead` the tp*head destination elements are one contiguous run too.  The run is
-// staged in shared memory as [position*head + d][lead] with an odd row stride in
-// 32-bit words; a warp then reads one `lead` column for 32 consecutive (d, d+1)
-// pairs and writes 128 contiguous bytes.
+// staged in shared memory transposed, as tile[lead index][position*head + d], so
+// that both global sides move 16 bytes per thread and access: the staging side
+// scatters the 8 lead values of a piece with 2-byte shared-memory stores, the other
+// side reads 8 consecutive d of one lead index as one 16-byte piece.  The 16-byte
+// pieces of a row are XOR-swizzled by the row's group of 8, which keeps the 2-byte
+// accesses of a warp (4 row groups x 8 consecutive d) on distinct banks.
 //
 // Arithmetic matches the reference's kernels bit for bit: the transposition is
 // exact, RoPE is round(round(c*a) - round(s*b)) in fp32 (no fused multiply-add,
@@ -34,89 +37,106 @@ enum : int { PRO_PLAIN = 0, PRO_ROPE = 1, PRO_BIAS = 2 };
 
 constexpr int PRO_THREADS = 256;
 
-__host__ __device__ inline int pro_stride_words(int lead)
+// halfword index of element (row n, offset h) in the staged tile; `row` = halfwords
+// per row (tp*head), `swz` = 7 when rows hold whole groups of 8 pieces, else 0
+__device__ __forceinline__ int pro_at(int n, int h, int row, int swz)
 {
-    // words per staged row: lead/2 rounded up to an odd number
-    const int w = (lead + 1)/2;
-    return (w & 1) ? w : w + 1;
+    return n*row + ((((h >> 3) ^ ((n >> 3) & swz)) << 3) | (h & 7));
+}
+
+__device__ __forceinline__ uint32_t pro_bf16x2(float lo, float hi)
+{
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo))
+            | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
 }
 
 template<int MODE>
 __global__ void __launch_bounds__(PRO_THREADS)
-transpose_in_kernel(int lead, int head, Index npos, int tp, const bf16 *__restrict__ aux0,
+transpose_in_kernel(int lead, int head, Index npos, int tp, int swz, const bf16 *__restrict__ aux0,
         const bf16 *__restrict__ aux1, const bf16 *__restrict__ src, bf16 *__restrict__ dst)
 {
-    extern __shared__ uint32_t tile[];
-    const int sw = pro_stride_words(lead);
+    extern __shared__ __align__(16) uint16_t tile[];
+    const int row = tp*head;
     const Index nchunks = (npos + tp - 1)/tp;
-    const int hp = head/2;                                // (d, d+1) pairs per position
-    const int hp_shift = (hp & (hp - 1)) == 0 ? 31 - __clz(hp) : -1;
     for(Index c = blockIdx.x; c < nchunks; c += gridDim.x)
     {
         const Index pos0 = c*tp;
         const int np = (int)((npos - pos0) < tp ? (npos - pos0) : tp);
-        const int rows = np*head;
-        // ---- stage: contiguous run of rows*lead elements; 16 bytes per thread when a
-        // row holds whole 16-byte pieces, 4 bytes otherwise (e.g. 12 heads)
+        const int rows = np*head;                          // (position, d) pairs in this run
+        // ---- stage: contiguous run of rows*lead elements, lead index fastest
         if((lead & 7) == 0)
         {
             const uint4 *g = reinterpret_cast<const uint4 *>(src + pos0*(Index)head*lead);
-            const int nvec = rows*lead/8;
+            const int per = lead >> 3, nvec = rows*per;
             for(int v = threadIdx.x; v < nvec; v += PRO_THREADS)
             {
                 const uint4 x = g[v];
-                const int e = 8*v, row = e/lead, col = e - row*lead;
-                uint32_t *t = tile + row*sw + (col >> 1);
-                t[0] = x.x;
-                t[1] = x.y;
-                t[2] = x.z;
-                t[3] = x.w;
+                const int h = v/per, n0 = (v - h*per) << 3;
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for(int e = 0; e < 4; ++e)
+                {
+                    tile[pro_at(n0 + 2*e, h, row, swz)] = (uint16_t)(w[e] & 0xFFFFu);
+                    tile[pro_at(n0 + 2*e + 1, h, row, swz)] = (uint16_t)(w[e] >> 16);
+                }
             }
         }
         else
         {
             const uint32_t *g = reinterpret_cast<const uint32_t *>(src + pos0*(Index)head*lead);
-            const int nw = rows*lead/2, lw = lead/2;
+            const int per = lead >> 1, nw = rows*per;
             for(int v = threadIdx.x; v < nw; v += PRO_THREADS)
             {
-                const int row = v/lw;
-                tile[row*sw + (v - row*lw)] = g[v];
+                const uint32_t w = g[v];
+                const int h = v/per, n0 = (v - h*per) << 1;
+                tile[pro_at(n0, h, row, swz)] = (uint16_t)(w & 0xFFFFu);
+                tile[pro_at(n0 + 1, h, row, swz)] = (uint16_t)(w >> 16);
             }
         }
         __syncthreads();
-        // ---- emit: a warp takes one lead index at a time and walks its np*hp pairs
-        // = np*head contiguous destination elements
-        const int run = np*hp;
-        for(int n = threadIdx.x >> 5; n < lead; n += PRO_THREADS/32)
-        for(int rem = threadIdx.x & 31; rem < run; rem += 32)
+        // ---- emit: for every lead index a contiguous run of `rows` elements, 8 per thread
+        const int per_row = rows >> 3, total = lead*per_row;
+        for(int v = threadIdx.x; v < total; v += PRO_THREADS)
         {
-            const int pp = hp_shift >= 0 ? (rem >> hp_shift) : rem/hp, p = rem - pp*hp;
-            const int row = pp*head + 2*p;
-            const uint32_t w0 = tile[row*sw + (n >> 1)], w1 = tile[(row + 1)*sw + (n >> 1)];
-            const uint32_t h0 = (n & 1) ? (w0 >> 16) : (w0 & 0xFFFFu);
-            const uint32_t h1 = (n & 1) ? (w1 >> 16) : (w1 & 0xFFFFu);
-            uint32_t out = h0 | (h1 << 16);
+            const int n = v/per_row, h = (v - n*per_row) << 3;
+            const uint4 x = *reinterpret_cast<const uint4 *>(&tile[pro_at(n, h, row, swz)]);
+            uint32_t w[4] = {x.x, x.y, x.z, x.w};
             if(MODE == PRO_ROPE)
             {
-                const Index i = (pos0 + pp)*(Index)hp + p;      // index into sin / cos
-                const float s = __bfloat162float(aux0[i]), co = __bfloat162float(aux1[i]);
-                const float a = __uint_as_float(h0 << 16), b = __uint_as_float(h1 << 16);
-                const float x = __fsub_rn(__fmul_rn(co, a), __fmul_rn(s, b));
-                const float y = __fadd_rn(__fmul_rn(s, a), __fmul_rn(co, b));
-                out = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x))
-                        | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y)) << 16);
+                // (position, d/2) index of the first of this piece's four pairs
+                const Index i = (pos0*(Index)head + h) >> 1;
+                const uint2 sv = *reinterpret_cast<const uint2 *>(aux0 + i);
+                const uint2 cv = *reinterpret_cast<const uint2 *>(aux1 + i);
+                const uint32_t sw[2] = {sv.x, sv.y}, cw[2] = {cv.x, cv.y};
+#pragma unroll
+                for(int e = 0; e < 4; ++e)
+                {
+                    const uint32_t sb = sw[e >> 1], cb = cw[e >> 1];
+                    const float sn = __uint_as_float((e & 1) ? (sb & 0xFFFF0000u) : (sb << 16));
+                    const float co = __uint_as_float((e & 1) ? (cb & 0xFFFF0000u) : (cb << 16));
+                    const float a = __uint_as_float(w[e] << 16);
+                    const float b = __uint_as_float(w[e] & 0xFFFF0000u);
+                    w[e] = pro_bf16x2(__fsub_rn(__fmul_rn(co, a), __fmul_rn(sn, b)),
+                            __fadd_rn(__fmul_rn(sn, a), __fmul_rn(co, b)));
+                }
             }
             else if(MODE == PRO_BIAS)
             {
-                const uint32_t bw = *reinterpret_cast<const uint32_t *>(
-                        aux0 + (Index)n*head + 2*p);            // bias[d, n], d fastest
-                const float x = __fadd_rn(__uint_as_float(h0 << 16), __uint_as_float(bw << 16));
-                const float y = __fadd_rn(__uint_as_float(h1 << 16),
-                        __uint_as_float(bw & 0xFFFF0000u));
-                out = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x))
-                        | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y)) << 16);
+                // bias[d, n], d fastest; the piece lies inside one position
+                const int d = h % head;
+                const uint4 bv = *reinterpret_cast<const uint4 *>(aux0 + (Index)n*head + d);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for(int e = 0; e < 4; ++e)
+                {
+                    w[e] = pro_bf16x2(
+                            __fadd_rn(__uint_as_float(w[e] << 16), __uint_as_float(bw[e] << 16)),
+                            __fadd_rn(__uint_as_float(w[e] & 0xFFFF0000u),
+                                    __uint_as_float(bw[e] & 0xFFFF0000u)));
+                }
             }
-            *reinterpret_cast<uint32_t *>(dst + (Index)n*npos*head + pos0*(Index)head + 2*rem) = out;
+            *reinterpret_cast<uint4 *>(dst + (Index)n*npos*head + pos0*(Index)head + h) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
         }
         __syncthreads();
     }
@@ -124,49 +144,51 @@ transpose_in_kernel(int lead, int head, Index npos, int tp, const bf16 *__restri
 
 // dst[n, d, pos] = src[d, pos, n]: the inverse layout change.
 __global__ void __launch_bounds__(PRO_THREADS)
-transpose_out_kernel(int lead, int head, Index npos, int tp, const bf16 *__restrict__ src,
+transpose_out_kernel(int lead, int head, Index npos, int tp, int swz, const bf16 *__restrict__ src,
         bf16 *__restrict__ dst)
 {
-    extern __shared__ uint32_t tile[];
-    uint16_t *tile16 = reinterpret_cast<uint16_t *>(tile);
-    const int sw = pro_stride_words(lead);
+    extern __shared__ __align__(16) uint16_t tile[];
+    const int row = tp*head;
     const Index nchunks = (npos + tp - 1)/tp;
-    const int hp = head/2;
     for(Index c = blockIdx.x; c < nchunks; c += gridDim.x)
     {
         const Index pos0 = c*tp;
         const int np = (int)((npos - pos0) < tp ? (npos - pos0) : tp);
         const int rows = np*head;
-        const int run = np*hp;
-        for(int n = threadIdx.x >> 5; n < lead; n += PRO_THREADS/32)
-        for(int rem = threadIdx.x & 31; rem < run; rem += 32)
+        const int per_row = rows >> 3, total = lead*per_row;
+        for(int v = threadIdx.x; v < total; v += PRO_THREADS)
         {
-            const uint32_t w = *reinterpret_cast<const uint32_t *>(
-                    src + (Index)n*npos*head + pos0*(Index)head + 2*rem);
-            const int row = 2*rem;                               // = pp*head + 2*p
-            tile16[2*(row*sw) + n] = (uint16_t)(w & 0xFFFFu);
-            tile16[2*((row + 1)*sw) + n] = (uint16_t)(w >> 16);
+            const int n = v/per_row, h = (v - n*per_row) << 3;
+            *reinterpret_cast<uint4 *>(&tile[pro_at(n, h, row, swz)]) =
+                    *reinterpret_cast<const uint4 *>(src + (Index)n*npos*head + pos0*(Index)head + h);
         }
         __syncthreads();
         if((lead & 7) == 0)
         {
             uint4 *g = reinterpret_cast<uint4 *>(dst + pos0*(Index)head*lead);
-            const int nvec = rows*lead/8;
+            const int per = lead >> 3, nvec = rows*per;
             for(int v = threadIdx.x; v < nvec; v += PRO_THREADS)
             {
-                const int e = 8*v, row = e/lead, col = e - row*lead;
-                const uint32_t *t = tile + row*sw + (col >> 1);
-                g[v] = make_uint4(t[0], t[1], t[2], t[3]);
+                const int h = v/per, n0 = (v - h*per) << 3;
+                uint32_t w[4];
+#pragma unroll
+                for(int e = 0; e < 4; ++e)
+                {
+                    w[e] = (uint32_t)tile[pro_at(n0 + 2*e, h, row, swz)]
+                            | ((uint32_t)tile[pro_at(n0 + 2*e + 1, h, row, swz)] << 16);
+                }
+                g[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
         else
         {
             uint32_t *g = reinterpret_cast<uint32_t *>(dst + pos0*(Index)head*lead);
-            const int nw = rows*lead/2, lw = lead/2;
+            const int per = lead >> 1, nw = rows*per;
             for(int v = threadIdx.x; v < nw; v += PRO_THREADS)
             {
-                const int row = v/lw;
-                g[v] = tile[row*sw + (v - row*lw)];
+                const int h = v/per, n0 = (v - h*per) << 1;
+                g[v] = (uint32_t)tile[pro_at(n0, h, row, swz)]
+                        | ((uint32_t)tile[pro_at(n0 + 1, h, row, swz)] << 16);
             }
         }
         __syncthreads();
@@ -175,7 +197,7 @@ transpose_out_kernel(int lead, int head, Index npos, int tp, const bf16 *__restr
 
 struct ProPlan
 {
-    int tp;
+    int tp, swz;
     size_t smem;
     unsigned grid;
 };
@@ -183,8 +205,9 @@ struct ProPlan
 static int pro_check(int64_t lead, int64_t head, int64_t seq, int64_t batch)
 {
     if(lead < 0 || head < 0 || seq < 0 || batch < 0) return NNTILE_B200_E_BADARG;
-    // two `lead` indices per 32-bit word and (d, d+1) pairs
-    if(lead % 2 != 0 || head % 2 != 0 || lead > 1024 || head > 1024) return NNTILE_B200_E_SHAPE;
+    // two `lead` indices per 32-bit word; a 16-byte piece of 8 head elements must not
+    // straddle two positions
+    if(lead % 2 != 0 || head % 8 != 0 || lead > 1024 || head > 1024) return NNTILE_B200_E_SHAPE;
     if(seq*batch >= ((int64_t)1 << 40)) return NNTILE_B200_E_SHAPE;
     return NNTILE_B200_OK;
 }
@@ -192,14 +215,16 @@ static int pro_check(int64_t lead, int64_t head, int64_t seq, int64_t batch)
 static ProPlan pro_plan(int lead, int head, Index npos)
 {
     ProPlan p;
-    const size_t row_bytes = (size_t)pro_stride_words(lead)*4;
-    // positions per chunk: up to about 32 KB of staging, at least one position
-    int tp = (int)((size_t)32768/(row_bytes*head));
+    // positions per chunk: about 32 KB of staging, rows of whole groups of 8 pieces
+    // (64 elements) when the head size allows it
+    int tp = (int)((size_t)32768/((size_t)lead*head*2));
     if(tp < 1) tp = 1;
-    if(tp > 8) tp = 8;
+    if(tp > 16) tp = 16;
     if((Index)tp > npos) tp = (int)npos;
+    while(tp > 1 && (tp*head) % 64 != 0) --tp;
     p.tp = tp;
-    p.smem = row_bytes*head*tp;
+    p.swz = (tp*head) % 64 == 0 ? 7 : 0;
+    p.smem = (size_t)lead*tp*head*2;
     const Index nchunks = (npos + tp - 1)/tp;
     const Index cap = 148*6;
     p.grid = (unsigned)(nchunks < cap ? nchunks : cap);
@@ -227,21 +252,24 @@ extern "C" int nntile_b200_transpose_rope_bf16(nntile_b200_stream_t stream, int6
     const Index npos = seq*batch;
     if(lead == 0 || head == 0 || npos == 0) return NNTILE_B200_OK;
     if(!src || !dst || ((sin == nullptr) != (cos == nullptr))) return NNTILE_B200_E_BADARG;
-    if(!aligned16(src) || !aligned16(dst)) return NNTILE_B200_E_ALIGN;
+    if(!aligned16(src) || !aligned16(dst) || (sin && (!aligned16(sin) || !aligned16(cos))))
+    {
+        return NNTILE_B200_E_ALIGN;
+    }
     const ProPlan p = pro_plan((int)lead, (int)head, npos);
     if(p.smem > 200*1024) return NNTILE_B200_E_SHAPE;
     if(sin)
     {
         if(!pro_optin(transpose_in_kernel<PRO_ROPE>, p.smem)) return NNTILE_B200_E_LAUNCH;
         transpose_in_kernel<PRO_ROPE><<<p.grid, PRO_THREADS, p.smem, as_stream(stream)>>>(
-                (int)lead, (int)head, npos, p.tp, (const bf16 *)sin, (const bf16 *)cos,
+                (int)lead, (int)head, npos, p.tp, p.swz, (const bf16 *)sin, (const bf16 *)cos,
                 (const bf16 *)src, (bf16 *)dst);
     }
     else
     {
         if(!pro_optin(transpose_in_kernel<PRO_PLAIN>, p.smem)) return NNTILE_B200_E_LAUNCH;
         transpose_in_kernel<PRO_PLAIN><<<p.grid, PRO_THREADS, p.smem, as_stream(stream)>>>(
-                (int)lead, (int)head, npos, p.tp, nullptr, nullptr, (const bf16 *)src,
+                (int)lead, (int)head, npos, p.tp, p.swz, nullptr, nullptr, (const bf16 *)src,
                 (bf16 *)dst);
     }
     return launch_status();
@@ -255,8 +283,7 @@ extern "C" int nntile_b200_transpose_bias_bf16(nntile_b200_stream_t stream, int6
     const Index npos = seq*batch;
     if(lead == 0 || head == 0 || npos == 0) return NNTILE_B200_OK;
     if(!src || !dst || !bias) return NNTILE_B200_E_BADARG;
-    if(!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 3u)
-            || (reinterpret_cast<uintptr_t>(bias) & 3u))
+    if(!aligned16(src) || !aligned16(dst) || !aligned16(bias))
     {
         return NNTILE_B200_E_ALIGN;
     }
@@ -264,7 +291,7 @@ extern "C" int nntile_b200_transpose_bias_bf16(nntile_b200_stream_t stream, int6
     if(p.smem > 200*1024) return NNTILE_B200_E_SHAPE;
     if(!pro_optin(transpose_in_kernel<PRO_BIAS>, p.smem)) return NNTILE_B200_E_LAUNCH;
     transpose_in_kernel<PRO_BIAS><<<p.grid, PRO_THREADS, p.smem, as_stream(stream)>>>((int)lead,
-            (int)head, npos, p.tp, (const bf16 *)bias, nullptr, (const bf16 *)src, (bf16 *)dst);
+            (int)head, npos, p.tp, p.swz, (const bf16 *)bias, nullptr, (const bf16 *)src, (bf16 *)dst);
     return launch_status();
 }
 
@@ -281,6 +308,6 @@ extern "C" int nntile_b200_transpose_heads_back_bf16(nntile_b200_stream_t stream
     if(p.smem > 200*1024) return NNTILE_B200_E_SHAPE;
     if(!pro_optin(transpose_out_kernel, p.smem)) return NNTILE_B200_E_LAUNCH;
     transpose_out_kernel<<<p.grid, PRO_THREADS, p.smem, as_stream(stream)>>>((int)lead, (int)head,
-            npos, p.tp, (const bf16 *)src, (bf16 *)dst);
+            npos, p.tp, p.swz, (const bf16 *)src, (bf16 *)dst);
     return launch_status();
 }
