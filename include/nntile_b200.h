@@ -9,7 +9,8 @@
  *   - all pointers are DEVICE pointers owned by the caller for the lifetime of
  *     the enqueued work; the library allocates nothing;
  *   - arrays are Fortran order (first index fastest), fp32 or bfloat16
- *     (bit-compatible with nntile::bf16_t / __nv_bfloat16);
+ *     (bit-compatible with nntile::bf16_t / __nv_bfloat16); the fused pair also
+ *     takes IEEE half (nntile::fp16_t / __half);
  *   - the return value is a status: 0 = enqueued, negative = rejected before any
  *     launch (see NNTILE_B200_E_*).  Nothing is thrown and nothing is printed.
  *
@@ -229,6 +230,56 @@ int nntile_b200_flash_sdpa_read_status(nntile_b200_stream_t stream, const void *
  * copy, so that one wait runs out, the status word becomes non-zero and the kernel
  * returns normally.  Nothing traps or spins; used by the test of the failure report. */
 void nntile_b200_test_arm_wait_timeout(void);
+
+/* IEEE half (nntile::fp16_t, bit-compatible with __half) forms of every fused-pair
+ * entry point above and of the tensor-level loops below: same arguments, contracts,
+ * shapes and status word; the mask holds fp16 values (0, -inf = 0xFC00, or any finite
+ * bias); P, dS and all outputs are rounded to fp16 where the bfloat16 forms round to
+ * bf16.  The reference instantiates its codelets and cuDNN wrappers for both types
+ * (src/starpu/flash_sdpa_fwd_cudnn.cc:292-293, src/starpu/flash_sdpa_bwd_cudnn.cc,
+ * src/kernel/flash_sdpa_fwd_cudnn/cuda.cc:53-63). */
+int nntile_b200_flash_sdpa_fwd_fp16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q,
+        const void *mask, float *scratch_lse, const void *V, void *scratch_A,
+        float *lse, void *A);
+int nntile_b200_flash_sdpa_bwd_fp16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, const void *K, const void *Q, const void *V,
+        const void *A, const void *dA, const void *mask, const float *lse,
+        void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ,
+        void *dV);
+int nntile_b200_flash_sdpa_fwd_gqa_fp16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
+        const void *Q, const void *mask, const void *V, float *lse, void *A,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_flash_sdpa_bwd_gqa_fp16(nntile_b200_stream_t stream, int64_t seq,
+        int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
+        const void *Q, const void *V, const void *A, const void *dA, const void *mask,
+        const float *lse, void *dK, void *dQ, void *dV, void *scratch,
+        size_t scratch_bytes);
+int nntile_b200_tensor_flash_sdpa_fwd_fp16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *mask_tiles,
+        float *const *lse_tiles, const void *const *V_tiles, void *const *A_tiles,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_tensor_flash_sdpa_bwd_fp16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *V_tiles,
+        const void *const *A_tiles, const void *const *dA_tiles,
+        const void *const *mask_tiles, const float *const *lse_tiles,
+        void *const *dK_tiles, void *const *dQ_tiles, void *const *dV_tiles,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_tensor_flash_sdpa_fwd_gqa_fp16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *mask_tiles,
+        float *const *lse_tiles, const void *const *V_tiles, void *const *A_tiles,
+        void *scratch, size_t scratch_bytes);
+int nntile_b200_tensor_flash_sdpa_bwd_gqa_fp16(nntile_b200_stream_t stream,
+        const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
+        const void *const *Q_tiles, const void *const *V_tiles,
+        const void *const *A_tiles, const void *const *dA_tiles,
+        const void *const *mask_tiles, const float *const *lse_tiles,
+        void *const *dK_tiles, void *const *dQ_tiles, void *const *dV_tiles,
+        void *scratch, size_t scratch_bytes);
 
 /* Which implementation nntile_b200_flash_sdpa_{fwd,bwd}_bf16 pick for a shape:
  * 2 = tcgen05/TMEM/TMA kernel, 1 = generic CUDA kernel, 0 = rejected. */

@@ -30,6 +30,7 @@ using Index = std::int64_t;
 using Scalar = float;
 struct fp32_t { float value; };
 struct bf16_t { std::uint16_t value; };
+struct fp16_t { std::uint16_t value; };
 struct bool_t { bool value; };
 // transposition flag of the reference's GEMM wrappers (include/nntile/constants.hh)
 struct TransOp
@@ -54,6 +55,8 @@ template<typename T>
 inline constexpr bool is_fp32 = std::is_same_v<T, nntile::fp32_t>;
 template<typename T>
 inline constexpr bool is_bf16 = std::is_same_v<T, nntile::bf16_t>;
+template<typename T>
+inline constexpr bool is_fp16 = std::is_same_v<T, nntile::fp16_t>;
 } // namespace nntile_b200
 
 #define NNTILE_B200_DISPATCH(T, NAME, ...) \
@@ -182,7 +185,7 @@ void gemm(cublasHandle_t handle, TransOp transA, TransOp transB, Index m, Index 
 } // namespace cublas
 
 // The fused pair: pointer order of the reference's execute_graph, stream instead of
-// the cuDNN handle and graph.  bf16 only (fp32 is rejected by the reference too).
+// the cuDNN handle and graph.  bf16 and fp16 (fp32 is rejected by the reference too).
 namespace flash_sdpa_fwd
 {
 template<typename T>
@@ -190,8 +193,10 @@ void cuda(cudaStream_t stream, Index seq, Index head, Index batch, const T *K, c
         const T *mask, fp32_t *scratch_logsumexp, const T *V, T *scratch_A, fp32_t *logsumexp,
         T *A) noexcept
 {
-    static_assert(nntile_b200::is_bf16<T>, "the fused path takes bf16");
-    nntile_b200::last_status() = nntile_b200_flash_sdpa_fwd_bf16(stream, seq, head, batch, K, Q,
+    static_assert(nntile_b200::is_bf16<T> || nntile_b200::is_fp16<T>,
+            "the fused path takes bf16 or fp16");
+    nntile_b200::last_status() = (nntile_b200::is_fp16<T> ? nntile_b200_flash_sdpa_fwd_fp16
+            : nntile_b200_flash_sdpa_fwd_bf16)(stream, seq, head, batch, K, Q,
             mask, reinterpret_cast<float *>(scratch_logsumexp), V, scratch_A,
             reinterpret_cast<float *>(logsumexp), A);
 }
@@ -204,8 +209,10 @@ void cuda(cudaStream_t stream, Index seq, Index head, Index batch, const T *K, c
         const T *V, const T *A, const T *dA, const T *mask, const fp32_t *logsumexp,
         T *scratch_dK, T *scratch_dQ, T *scratch_dV, T *dK, T *dQ, T *dV) noexcept
 {
-    static_assert(nntile_b200::is_bf16<T>, "the fused path takes bf16");
-    nntile_b200::last_status() = nntile_b200_flash_sdpa_bwd_bf16(stream, seq, head, batch, K, Q,
+    static_assert(nntile_b200::is_bf16<T> || nntile_b200::is_fp16<T>,
+            "the fused path takes bf16 or fp16");
+    nntile_b200::last_status() = (nntile_b200::is_fp16<T> ? nntile_b200_flash_sdpa_bwd_fp16
+            : nntile_b200_flash_sdpa_bwd_bf16)(stream, seq, head, batch, K, Q,
             V, A, dA, mask, reinterpret_cast<const float *>(logsumexp), scratch_dK, scratch_dQ,
             scratch_dV, dK, dQ, dV);
 }

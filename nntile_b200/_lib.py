@@ -56,6 +56,10 @@ SIGNATURES = {
     "nntile_b200_transpose_bias_bf16": ([vp] + [i64]*4 + [vp]*3, ctypes.c_int),
     "nntile_b200_transpose_heads_back_bf16": ([vp] + [i64]*4 + [vp]*2, ctypes.c_int),
 }
+for _name in ("flash_sdpa_fwd", "flash_sdpa_bwd", "flash_sdpa_fwd_gqa", "flash_sdpa_bwd_gqa",
+              "tensor_flash_sdpa_fwd", "tensor_flash_sdpa_bwd", "tensor_flash_sdpa_fwd_gqa",
+              "tensor_flash_sdpa_bwd_gqa"):
+    SIGNATURES[f"nntile_b200_{_name}_fp16"] = SIGNATURES[f"nntile_b200_{_name}_bf16"]
 for _name, _args in _TYPED.items():
     for _sfx in ("fp32", "bf16"):
         SIGNATURES[f"nntile_b200_{_name}_{_sfx}"] = (_args, ctypes.c_int)

@@ -25,6 +25,11 @@ SOURCES = [
     "flash_fwd_sm100.cu", "flash_bwd_sm100.cu", "host_tensor.cu", "gemm_cublas.cu",
     "sdpa_prologue.cu",
 ]
+# the fused-attention sources are compiled a second time for IEEE half (elem.cuh)
+FP16_SOURCES = [
+    "flash_generic.cu", "flash_api.cu", "flash_fwd_sm100.cu", "flash_bwd_sm100.cu",
+    "host_tensor.cu",
+]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
@@ -50,11 +55,13 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def _compile(src: str, force: bool) -> str:
-    obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+def _compile(job, force: bool) -> str:
+    src, fp16 = job
+    obj = os.path.join(OBJ_DIR, src.replace(".cu", "_fp16.o" if fp16 else ".o"))
     if force or _stale(obj, _deps(src)):
         log = obj + ".log"
-        cmd = [_nvcc()] + NVCC_FLAGS + ["-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [_nvcc()] + NVCC_FLAGS + (["-DNB200_FP16"] if fp16 else []) \
+            + ["-c", os.path.join(CSRC, src), "-o", obj]
         res = subprocess.run(cmd, capture_output=True, text=True)
         with open(log, "w") as f:
             f.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
@@ -65,9 +72,9 @@ def _compile(src: str, force: bool) -> str:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ_DIR, exist_ok=True)
-    srcs = [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
-    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile(s, force), srcs))
+    jobs = [(s, False) for s in SOURCES] + [(s, True) for s in FP16_SOURCES]
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+        objs = list(ex.map(lambda j: _compile(j, force), jobs))
     if force or _stale(LIB, objs):
         cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode",
                "arch=compute_100a,code=sm_100a", "-ldl"]

@@ -2,16 +2,18 @@
 // and the kernels that implement them.
 #pragma once
 #include "common.cuh"
+#include "elem.cuh"
 
 namespace nb200 {
+inline namespace NB200_ELEM_NS {
 
 // Generic CUDA-core kernels (flash_generic.cu): any seq, head <= 256.
-int flash_fwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A);
-int flash_bwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
-        const float *lse, float *delta, bf16 *dK, bf16 *dQ, bf16 *dV);
-int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const bf16 *A, const bf16 *dA,
+int flash_fwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *mask, const elem_t *V, float *lse, elem_t *A);
+int flash_bwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *V, const elem_t *A, const elem_t *dA, const elem_t *mask,
+        const float *lse, float *delta, elem_t *dK, elem_t *dQ, elem_t *dV);
+int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const elem_t *A, const elem_t *dA,
         float *delta);
 
 // tcgen05 / TMEM / TMA kernels (flash_fwd_sm100.cu, flash_bwd_sm100.cu):
@@ -41,7 +43,7 @@ enum : int
     BWD_CLASSIFY = 1,   // classify the mask into `cls`, clear `status`
     BWD_PREP = 2,       // delta, lse2, clear the accumulator
     BWD_MAIN = 4,       // the tcgen05 kernel: dK, dV += ..., accumulator += dQ
-    BWD_FINISH = 8,     // dQ += bf16(scale * accumulator)
+    BWD_FINISH = 8,     // dQ += elem_t(scale * accumulator)
     BWD_ALL = 15
 };
 
@@ -59,13 +61,13 @@ bool flash_fwd_sm100_supports(Index seq, Index head, Index batch);
 // K, V (and dK, dV) may be shared by `kv_group` consecutive groups of `kv_batch`
 // batch entries: entry b uses K/V entry (b % kv_batch) + kv_batch*(b/(kv_batch*kv_group)).
 // kv_group = 1, kv_batch = batch is the plain one-to-one case.
-int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A,
+int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *mask, const elem_t *V, float *lse, elem_t *A,
         const FwdAux &aux, Index kv_group, Index kv_batch);
 bool flash_bwd_sm100_supports(Index seq, Index head, Index batch);
-int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
-        const float *lse, const BwdAux &aux, bf16 *dK, bf16 *dQ, bf16 *dV, Index kv_group,
+int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *V, const elem_t *A, const elem_t *dA, const elem_t *mask,
+        const float *lse, const BwdAux &aux, elem_t *dK, elem_t *dQ, elem_t *dV, Index kv_group,
         Index kv_batch);
 // Layout the tile-level entry points give the three scratch buffers of a backward
 // task (status + class table + delta + lse2 in scratch_dV, the accumulator halves
@@ -138,7 +140,8 @@ __device__ __forceinline__ void group_decode(unsigned cta, int nunits, int batch
 
 // Classify every block of `mask` into `cls` and, when `status` is not null, clear
 // that status word (flash_fwd_sm100.cu).
-int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *cls,
+int launch_mask_classify(cudaStream_t s, int seq, const elem_t *mask, uint8_t *cls,
         uint32_t *status);
 
+} // inline namespace
 } // namespace nb200

@@ -12,6 +12,7 @@ static int check_common(int64_t seq, int64_t head, int64_t batch)
     return NNTILE_B200_OK;
 }
 
+#ifndef NB200_FP16
 extern "C" int nntile_b200_flash_sdpa_fwd_path(int64_t seq, int64_t head, int64_t batch)
 {
     if(check_common(seq, head, batch) != NNTILE_B200_OK) return 0;
@@ -24,7 +25,10 @@ extern "C" int nntile_b200_flash_sdpa_bwd_path(int64_t seq, int64_t head, int64_
     return flash_bwd_sm100_supports(seq, head, batch) ? 2 : 1;
 }
 
+#endif // NB200_FP16
+
 namespace nb200 {
+inline namespace NB200_ELEM_NS {
 
 int flash_fwd_task(cudaStream_t stream, Index seq, Index head, Index batch, const void *K,
         const void *Q, const void *mask, const void *V, void *scratch_A, float *lse, void *A,
@@ -51,7 +55,7 @@ int flash_fwd_task(cudaStream_t stream, Index seq, Index head, Index batch, cons
         {
             // status word + class table at the start of the task's scratch buffer
             const size_t nblk = (size_t)(seq/128);
-            if((size_t)seq*head*batch*sizeof(bf16) < CLS_OFFSET + nblk*nblk)
+            if((size_t)seq*head*batch*sizeof(elem_t) < CLS_OFFSET + nblk*nblk)
             {
                 return NNTILE_B200_E_SCRATCH;
             }
@@ -60,11 +64,11 @@ int flash_fwd_task(cudaStream_t stream, Index seq, Index head, Index batch, cons
             aux.cls = sc + CLS_OFFSET;
             aux.classify = true;
         }
-        return flash_fwd_sm100(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
-                (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A, aux, 1, batch);
+        return flash_fwd_sm100(stream, seq, head, batch, (const elem_t *)K, (const elem_t *)Q,
+                (const elem_t *)mask, (const elem_t *)V, lse, (elem_t *)A, aux, 1, batch);
     }
-    return flash_fwd_generic(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
-            (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A);
+    return flash_fwd_generic(stream, seq, head, batch, (const elem_t *)K, (const elem_t *)Q,
+            (const elem_t *)mask, (const elem_t *)V, lse, (elem_t *)A);
 }
 
 int flash_bwd_task(cudaStream_t stream, Index seq, Index head, Index batch, const void *K,
@@ -100,18 +104,19 @@ int flash_bwd_task(cudaStream_t stream, Index seq, Index head, Index batch, cons
         }
         const BwdAux aux = bwd_aux ? *bwd_aux
                 : bwd_aux_from_scratch(seq, batch, scratch_dK, scratch_dQ, scratch_dV);
-        return flash_bwd_sm100(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
-                (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA, (const bf16 *)mask, lse, aux,
-                (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV, 1, batch);
+        return flash_bwd_sm100(stream, seq, head, batch, (const elem_t *)K, (const elem_t *)Q,
+                (const elem_t *)V, (const elem_t *)A, (const elem_t *)dA, (const elem_t *)mask, lse, aux,
+                (elem_t *)dK, (elem_t *)dQ, (elem_t *)dV, 1, batch);
     }
-    return flash_bwd_generic(stream, seq, head, batch, (const bf16 *)K, (const bf16 *)Q,
-            (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA, (const bf16 *)mask, lse,
-            (float *)scratch_dV, (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV);
+    return flash_bwd_generic(stream, seq, head, batch, (const elem_t *)K, (const elem_t *)Q,
+            (const elem_t *)V, (const elem_t *)A, (const elem_t *)dA, (const elem_t *)mask, lse,
+            (float *)scratch_dV, (elem_t *)dK, (elem_t *)dQ, (elem_t *)dV);
 }
 
+} // inline namespace
 } // namespace nb200
 
-extern "C" int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+extern "C" int NB200_SFX(nntile_b200_flash_sdpa_fwd)(nntile_b200_stream_t stream, int64_t seq,
         int64_t head, int64_t batch, const void *K, const void *Q, const void *mask,
         float *scratch_lse, const void *V, void *scratch_A, float *lse, void *A)
 {
@@ -120,7 +125,7 @@ extern "C" int nntile_b200_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream, int6
             nullptr);
 }
 
-extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int64_t seq,
+extern "C" int NB200_SFX(nntile_b200_flash_sdpa_bwd)(nntile_b200_stream_t stream, int64_t seq,
         int64_t head, int64_t batch, const void *K, const void *Q, const void *V,
         const void *A, const void *dA, const void *mask, const float *lse,
         void *scratch_dK, void *scratch_dQ, void *scratch_dV, void *dK, void *dQ, void *dV)
@@ -129,6 +134,7 @@ extern "C" int nntile_b200_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream, int6
             scratch_dK, scratch_dQ, scratch_dV, dK, dQ, dV, nullptr);
 }
 
+#ifndef NB200_FP16
 // The status word of the fused kernels sits in the first four bytes of the scratch
 // buffer that carries a task's bookkeeping; this reads it back after the stream
 // has drained.
@@ -146,6 +152,8 @@ extern "C" int nntile_b200_flash_sdpa_read_status(nntile_b200_stream_t stream,
     return NNTILE_B200_OK;
 }
 
+#endif // NB200_FP16
+
 // ------------------------------------------------------------ grouped-query form
 // Q, A, dA, dQ: [head, seq, batch, group, kv_heads]; K, V, dK, dV: [head, seq, batch,
 // kv_heads] (not replicated over the group).  tcgen05 kernels only.
@@ -155,16 +163,19 @@ static int check_gqa(int64_t seq, int64_t head, int64_t batch, int64_t group, in
     return NNTILE_B200_OK;
 }
 
+#ifndef NB200_FP16
 extern "C" size_t nntile_b200_flash_sdpa_gqa_scratch_bytes(int64_t seq, int64_t head,
         int64_t batch, int64_t group, int64_t kv_heads)
 {
     if(check_gqa(seq, head, batch, group, kv_heads) != NNTILE_B200_OK) return 0;
     // status word + class table + delta + lse*log2e in a region the size of one
-    // bf16 tensor, then the fp32 dQ accumulator
+    // elem_t tensor, then the fp32 dQ accumulator
     return (size_t)seq*head*batch*group*kv_heads*6;
 }
 
-extern "C" int nntile_b200_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
+#endif // NB200_FP16
+
+extern "C" int NB200_SFX(nntile_b200_flash_sdpa_fwd_gqa)(nntile_b200_stream_t stream, int64_t seq,
         int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
         const void *Q, const void *mask, const void *V, float *lse, void *A, void *scratch,
         size_t scratch_bytes)
@@ -184,12 +195,12 @@ extern "C" int nntile_b200_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream, 
     if(scratch_bytes < CLS_OFFSET + nblk*nblk) return NNTILE_B200_E_SCRATCH;
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     const FwdAux aux = {reinterpret_cast<uint32_t *>(sc), sc + CLS_OFFSET, true};
-    return flash_fwd_sm100(as_stream(stream), seq, head, slices, (const bf16 *)K,
-            (const bf16 *)Q, (const bf16 *)mask, (const bf16 *)V, lse, (bf16 *)A, aux, group,
+    return flash_fwd_sm100(as_stream(stream), seq, head, slices, (const elem_t *)K,
+            (const elem_t *)Q, (const elem_t *)mask, (const elem_t *)V, lse, (elem_t *)A, aux, group,
             batch);
 }
 
-extern "C" int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, int64_t seq,
+extern "C" int NB200_SFX(nntile_b200_flash_sdpa_bwd_gqa)(nntile_b200_stream_t stream, int64_t seq,
         int64_t head, int64_t batch, int64_t group, int64_t kv_heads, const void *K,
         const void *Q, const void *V, const void *A, const void *dA, const void *mask,
         const float *lse, void *dK, void *dQ, void *dV, void *scratch, size_t scratch_bytes)
@@ -213,10 +224,10 @@ extern "C" int nntile_b200_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream, 
     {
         return NNTILE_B200_E_ALIGN;
     }
-    const size_t part = (size_t)seq*head*slices*2;        // one bf16 tensor of Q's shape
+    const size_t part = (size_t)seq*head*slices*2;        // one elem_t tensor of Q's shape
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     const BwdAux aux = bwd_aux_from_scratch(seq, slices, sc + 2*part, sc + part, sc);
-    return flash_bwd_sm100(as_stream(stream), seq, head, slices, (const bf16 *)K,
-            (const bf16 *)Q, (const bf16 *)V, (const bf16 *)A, (const bf16 *)dA,
-            (const bf16 *)mask, lse, aux, (bf16 *)dK, (bf16 *)dQ, (bf16 *)dV, group, batch);
+    return flash_bwd_sm100(as_stream(stream), seq, head, slices, (const elem_t *)K,
+            (const elem_t *)Q, (const elem_t *)V, (const elem_t *)A, (const elem_t *)dA,
+            (const elem_t *)mask, lse, aux, (elem_t *)dK, (elem_t *)dQ, (elem_t *)dV, group, batch);
 }

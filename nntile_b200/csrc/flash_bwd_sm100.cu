@@ -4,7 +4,7 @@
 // Replaces, for head in {64, 128} and seq a multiple of 128, what
 // src/kernel/flash_sdpa_bwd_cudnn/cuda.cc:171-218 does with a cuDNN backward
 // graph into scratch followed by three add_inplace passes: gradients of one
-// (Q tile, K/V tile) task from the GIVEN A and lse, rounded to bf16 and ADDED
+// (Q tile, K/V tile) task from the GIVEN A and lse, rounded to elem_t and ADDED
 // into dK, dQ, dV.
 //
 // One CTA owns one block of 128 keys of one batch entry: K and V stay in shared
@@ -51,6 +51,7 @@
 #include "sm100.cuh"
 
 namespace nb200 {
+inline namespace NB200_ELEM_NS {
 
 using namespace sm100;
 
@@ -103,8 +104,8 @@ struct Smem
 // Also clears the fp32 dQ accumulator (split at half_rows over two buffers).  head/8
 // threads per row, 16 bytes of A and of dA per thread; head is 64 or 128.
 __global__ void __launch_bounds__(256)
-bwd_prep_kernel(int head, Index rows, Index half_rows, const bf16 *__restrict__ A,
-        const bf16 *__restrict__ dA, const float *__restrict__ lse,
+bwd_prep_kernel(int head, Index rows, Index half_rows, const elem_t *__restrict__ A,
+        const elem_t *__restrict__ dA, const float *__restrict__ lse,
         float *__restrict__ delta, float *__restrict__ lse2, float *__restrict__ acc_lo,
         float *__restrict__ acc_hi)
 {
@@ -121,9 +122,8 @@ bwd_prep_kernel(int head, Index rows, Index half_rows, const bf16 *__restrict__ 
 #pragma unroll
         for(int e = 0; e < 4; ++e)
         {
-            acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), acc);
-            acc = fmaf(__uint_as_float(aw[e] & 0xFFFF0000u), __uint_as_float(gw[e] & 0xFFFF0000u),
-                    acc);
+            acc = fmaf(elem_lo(aw[e]), elem_lo(gw[e]), acc);
+            acc = fmaf(elem_hi(aw[e]), elem_hi(gw[e]), acc);
         }
         float4 *z = reinterpret_cast<float4 *>(
                 (r < half_rows ? acc_lo + r*head : acc_hi + (r - half_rows)*head) + 8*piece);
@@ -146,10 +146,10 @@ bwd_prep_kernel(int head, Index rows, Index half_rows, const bf16 *__restrict__ 
     }
 }
 
-// dQ[r,h] += bf16(scale * acc[r,h]); the accumulator is split over two buffers.
+// dQ[r,h] += elem_t(scale * acc[r,h]); the accumulator is split over two buffers.
 __global__ void bwd_dq_finish_kernel(int head, Index rows, Index half_rows, float scale,
         const float *__restrict__ acc_lo, const float *__restrict__ acc_hi,
-        bf16 *__restrict__ dQ)
+        elem_t *__restrict__ dQ)
 {
     const Index total = rows*head/4, stride = (Index)gridDim.x*blockDim.x;
     for(Index x = (Index)blockIdx.x*blockDim.x + threadIdx.x; x < total; x += stride)
@@ -158,14 +158,12 @@ __global__ void bwd_dq_finish_kernel(int head, Index rows, Index half_rows, floa
         const float *src = r < half_rows ? acc_lo + e : acc_hi + (e - half_rows*head);
         const float4 a = *reinterpret_cast<const float4 *>(src);
         uint2 old = *reinterpret_cast<const uint2 *>(dQ + e);
-        const float o0 = __uint_as_float(old.x << 16), o1 = __uint_as_float(old.x & 0xFFFF0000u);
-        const float o2 = __uint_as_float(old.y << 16), o3 = __uint_as_float(old.y & 0xFFFF0000u);
-        const float g0 = __bfloat162float(__float2bfloat16_rn(a.x*scale));
-        const float g1 = __bfloat162float(__float2bfloat16_rn(a.y*scale));
-        const float g2 = __bfloat162float(__float2bfloat16_rn(a.z*scale));
-        const float g3 = __bfloat162float(__float2bfloat16_rn(a.w*scale));
-        old.x = pack_bf16x2(o0 + g0, o1 + g1);
-        old.y = pack_bf16x2(o2 + g2, o3 + g3);
+        const float o0 = elem_lo(old.x), o1 = elem_hi(old.x);
+        const float o2 = elem_lo(old.y), o3 = elem_hi(old.y);
+        const float g0 = elem_round(a.x*scale), g1 = elem_round(a.y*scale);
+        const float g2 = elem_round(a.z*scale), g3 = elem_round(a.w*scale);
+        old.x = pack_elem2(o0 + g0, o1 + g1);
+        old.y = pack_elem2(o2 + g2, o3 + g3);
         *reinterpret_cast<uint2 *>(dQ + e) = old;
     }
 }
@@ -189,7 +187,7 @@ __device__ __forceinline__ void load_tile(uint8_t *dst, const CUtensorMap *map, 
 template<int D>
 __device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, const uint8_t *a, const uint8_t *b)
 {
-    constexpr uint32_t idesc = idesc_bf16(BLK, BLK, 0, 0);
+    constexpr uint32_t idesc = idesc_16(BLK, BLK, 0, 0, ELEM_MMA_FORMAT);
     constexpr uint32_t hi = smem_desc_hi(1024);
     const uint32_t a_lo = smem_desc_lo(smem_u32(a), 16), b_lo = smem_desc_lo(smem_u32(b), 16);
 #pragma unroll
@@ -209,14 +207,14 @@ __device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, const uint8_t *a, 
     }
 }
 
-// C[128 x D] (+)= A B with A = bf16 [128 lanes x 128] in TMEM, stored as two
+// C[128 x D] (+)= A B with A = elem_t [128 lanes x 128] in TMEM, stored as two
 // 32-column pieces at a_tmem and a_tmem + 64, and B = [128 rows][D] tile read
 // MN-major (rows are the contraction index).
 template<int D>
 __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, const uint8_t *b,
         bool accumulate)
 {
-    constexpr uint32_t idesc = idesc_bf16(BLK, D, 0, 1);
+    constexpr uint32_t idesc = idesc_16(BLK, D, 0, 1, ELEM_MMA_FORMAT);
     constexpr uint32_t hi = smem_desc_hi(1024);
     const uint32_t b_lo = smem_desc_lo(smem_u32(b), BLK*128);
     if(accumulate)
@@ -242,7 +240,7 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, const
 template<int D>
 __device__ __forceinline__ void issue_dq(uint32_t d_tmem, const uint8_t *ds, const uint8_t *k)
 {
-    constexpr uint32_t idesc = idesc_bf16(BLK, D, 1, 1);
+    constexpr uint32_t idesc = idesc_16(BLK, D, 1, 1, ELEM_MMA_FORMAT);
     constexpr uint32_t hi = smem_desc_hi(1024);
     const uint32_t a_lo = smem_desc_lo(smem_u32(ds), BLK*128);
     const uint32_t b_lo = smem_desc_lo(smem_u32(k), BLK*128);
@@ -270,7 +268,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_dk,
         const __grid_constant__ CUtensorMap tmap_dv, int seq, int batch, int gsz, int kv_group,
         int kv_batch, float scale_log2,
-        float scale, const bf16 *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
+        float scale, const elem_t *__restrict__ mask, const uint8_t *__restrict__ cls_tab,
         const float *__restrict__ delta, const float *__restrict__ lse2,
         float *__restrict__ acc_lo, float *__restrict__ acc_hi, Index half_rows,
         uint32_t *status)
@@ -711,7 +709,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             const float4 *nl4 = reinterpret_cast<const float4 *>(&sm.stats[n & 1][0][64*h]);
             const float4 *nd4 = reinterpret_cast<const float4 *>(&sm.stats[n & 1][1][64*h]);
             // ---- phase A: P^T = exp2(S^T*c - lse2 [+ bias]) for this thread's 64 query
-            // columns, kept as packed bf16 in registers and written over the S^T
+            // columns, kept as packed elem_t in registers and written over the S^T
             // columns; needs S^T only, so it overlaps the MMAs of the previous block
             PROF_T(s0);
             ok = mbar_wait(&sm.s_full, (uint32_t)n & 1u, abort_flag);
@@ -753,7 +751,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll
                             for(int u = 0; u < 4; ++u)
                             {
-                                const float bias = __bfloat162float(
+                                const float bias = elem_to_f(
                                         mask[(size_t)(qb*BLK + qc + u)*seq + (size_t)kb*BLK + r]);
                                 x[u] = bias == -CUDART_INF_F ? -CUDART_INF_F
                                                              : fmaf(bias, LOG2E_F, x[u]);
@@ -762,8 +760,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         // all four on the MUFU unit: a cubic on the FMA pipe for part of
                         // them was measured slower (the warps are short of issue slots)
                         const float e2 = ex2(x[2]), e3 = ex2(x[3]);
-                        pk[c2][j >> 1] = pack_bf16x2(ex2(x[0]), ex2(x[1]));
-                        pk[c2][(j >> 1) + 1] = pack_bf16x2(e2, e3);
+                        pk[c2][j >> 1] = pack_elem2(ex2(x[0]), ex2(x[1]));
+                        pk[c2][(j >> 1) + 1] = pack_elem2(e2, e3);
                     }
                 }
             }
@@ -797,16 +795,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     const float4 nd = nd4[(32*c2 + j) >> 2];
                     const uint32_t w0 = pk[c2][j >> 1], w1 = pk[c2][(j >> 1) + 1];
                     float d[4];
-                    unpack_f32x2(fmul2(pack_f32x2(__uint_as_float(w0 << 16),
-                            __uint_as_float(w0 & 0xFFFF0000u)),
+                    unpack_f32x2(fmul2(pack_f32x2(elem_lo(w0), elem_hi(w0)),
                             fadd2(pack_f32x2(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])),
                                     pack_f32x2(nd.x, nd.y))), d[0], d[1]);
-                    unpack_f32x2(fmul2(pack_f32x2(__uint_as_float(w1 << 16),
-                            __uint_as_float(w1 & 0xFFFF0000u)),
+                    unpack_f32x2(fmul2(pack_f32x2(elem_lo(w1), elem_hi(w1)),
                             fadd2(pack_f32x2(__uint_as_float(dp[j + 2]), __uint_as_float(dp[j + 3])),
                                     pack_f32x2(nd.z, nd.w))), d[2], d[3]);
-                    pd[j >> 1] = pack_bf16x2(d[0], d[1]);
-                    pd[(j >> 1) + 1] = pack_bf16x2(d[2], d[3]);
+                    pd[j >> 1] = pack_elem2(d[0], d[1]);
+                    pd[(j >> 1) + 1] = pack_elem2(d[2], d[3]);
                 }
                 tmem_st16(dpt_tm + lane_sel + 64*h + 16*c2, pd);
                 // dS^T row r, query columns 64h+32c2 .. +31: four 16-byte pieces of
@@ -844,10 +840,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
         // ---- epilogue: dV (half 0) / dK (half 1) += accumulators ------------------
         // Each warp owns 32 key rows of dV (h = 0) or dK (h = 1).  The gradient is
-        // rounded to bf16 and written into the warp's part of the Q stage (dV) or dO
+        // rounded to elem_t and written into the warp's part of the Q stage (dV) or dO
         // stage (dK) that the LAST query block did not use, as 64-column panels with
         // 128-byte rows and the 128-byte swizzle of the tensor maps, and one lane
-        // hands the panels to the TMA unit as element-wise bf16 additions into dV /
+        // hands the panels to the TMA unit as element-wise elem_t additions into dV /
         // dK: the reference's "+=" without this SM reading the old values or
         // waiting for them.  That stage was last touched by the block before the
         // last one; its hand-back barrier is waited for first.
@@ -888,7 +884,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll
                     for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        w[e2] = pack_bf16x2(__uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2])*mult,
+                        w[e2] = pack_elem2(__uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2])*mult,
                                 __uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2 + 1])*mult);
                     }
                     *reinterpret_cast<uint4 *>(prow + ((g8 ^ (lane & 7)) << 4)) =
@@ -1010,9 +1006,9 @@ BwdAux bwd_aux_from_scratch(Index seq, Index batch, void *scratch_dK, void *scra
 
 template<int D>
 static int bwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index kv_batch,
-        const bf16 *K, const bf16 *Q,
-        const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask, const float *lse,
-        const BwdAux &aux, bf16 *dK, bf16 *dQ, bf16 *dV)
+        const elem_t *K, const elem_t *Q,
+        const elem_t *V, const elem_t *A, const elem_t *dA, const elem_t *mask, const float *lse,
+        const BwdAux &aux, elem_t *dK, elem_t *dQ, elem_t *dV)
 {
     using namespace bwd;
     const Index rows = batch*seq;
@@ -1039,12 +1035,12 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index
     {
         CUtensorMap tk, tv, tq, tg, tdk, tdv;
         const Index kv_rows = rows/kv_group;
-        if(!make_tmap_bf16_sw128(&tk, K, kv_rows, D, BLK)
-                || !make_tmap_bf16_sw128(&tv, V, kv_rows, D, BLK)
-                || !make_tmap_bf16_sw128(&tq, Q, rows, D, BLK)
-                || !make_tmap_bf16_sw128(&tg, dA, rows, D, BLK)
-                || !make_tmap_bf16_sw128(&tdk, dK, kv_rows, D, 32)
-                || !make_tmap_bf16_sw128(&tdv, dV, kv_rows, D, 32))
+        if(!make_tmap_16_sw128(&tk, K, kv_rows, D, BLK, ELEM_TMAP_TYPE)
+                || !make_tmap_16_sw128(&tv, V, kv_rows, D, BLK, ELEM_TMAP_TYPE)
+                || !make_tmap_16_sw128(&tq, Q, rows, D, BLK, ELEM_TMAP_TYPE)
+                || !make_tmap_16_sw128(&tg, dA, rows, D, BLK, ELEM_TMAP_TYPE)
+                || !make_tmap_16_sw128(&tdk, dK, kv_rows, D, 32, ELEM_TMAP_TYPE)
+                || !make_tmap_16_sw128(&tdv, dV, kv_rows, D, 32, ELEM_TMAP_TYPE))
         {
             return NNTILE_B200_E_LAUNCH;
         }
@@ -1061,7 +1057,7 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index
         {
             return NNTILE_B200_E_LAUNCH;
         }
-        // Q, K, V, dO, dK, dV (bf16) and the fp32 dQ accumulator of one batch entry
+        // Q, K, V, dO, dK, dV (elem_t) and the fp32 dQ accumulator of one batch entry
         const int gsz = l2_group_size(batch, (size_t)seq*D*(2*6 + 4));
         flash_bwd_kernel<D><<<(unsigned)(nblk*batch), THREADS, smem_bytes, s>>>(tk, tv, tq, tg,
                 tdk, tdv, (int)seq, (int)batch, gsz, (int)kv_group, (int)kv_batch, scale*LOG2E_F,
@@ -1081,9 +1077,9 @@ static int bwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index
     return NNTILE_B200_OK;
 }
 
-int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
-        const float *lse, const BwdAux &aux, bf16 *dK, bf16 *dQ, bf16 *dV, Index kv_group,
+int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *V, const elem_t *A, const elem_t *dA, const elem_t *mask,
+        const float *lse, const BwdAux &aux, elem_t *dK, elem_t *dQ, elem_t *dV, Index kv_group,
         Index kv_batch)
 {
     if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0 || !aux.status || !aux.cls
@@ -1098,4 +1094,5 @@ int flash_bwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf
                     dK, dQ, dV);
 }
 
+} // inline namespace
 } // namespace nb200

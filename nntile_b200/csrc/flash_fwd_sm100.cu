@@ -20,7 +20,7 @@
 //   warps 4-11  two softmax groups of 128 threads, one per query tile, one thread
 //               per query row: tcgen05.ld of the S row, bias, running max with a
 //               lazy rescale of O (only when the max grows by more than 2^8),
-//               exp2, bf16 P written back into the S columns, and at the end the
+//               exp2, elem_t P written back into the S columns, and at the end the
 //               normalisation, the merge with the stored (lse, A) and the store
 //               (staged through shared memory; a TMA store when nothing is merged).
 // During the set-up warp 1 allocates TMEM, warp 2 reads the status word and
@@ -42,6 +42,7 @@
 #include "sm100.cuh"
 
 namespace nb200 {
+inline namespace NB200_ELEM_NS {
 
 using namespace sm100;
 
@@ -70,7 +71,7 @@ constexpr float RESCALE_STEP = 8.0f;
 // grid (key block, query block), 256 threads; also clears the status word when one
 // is given.
 __global__ void __launch_bounds__(256)
-mask_classify_kernel(int seq, int nblk, const bf16 *__restrict__ mask, uint8_t *cls,
+mask_classify_kernel(int seq, int nblk, const elem_t *__restrict__ mask, uint8_t *cls,
         uint32_t *status)
 {
     const int kb = blockIdx.x, qb = blockIdx.y;
@@ -87,7 +88,7 @@ mask_classify_kernel(int seq, int nblk, const bf16 *__restrict__ mask, uint8_t *
         for(int e = 0; e < 8; ++e)
         {
             const uint32_t bits = (w[e >> 1] >> (16*(e & 1))) & 0xFFFFu;
-            const bool is_zero = (bits & 0x7FFFu) == 0u, is_ninf = bits == 0xFF80u;
+            const bool is_zero = (bits & 0x7FFFu) == 0u, is_ninf = bits == ELEM_NINF_BITS;
             zero &= is_zero;
             ninf &= is_ninf;
             causal &= (c16*8 + e > row) ? is_ninf : is_zero;
@@ -144,7 +145,7 @@ __device__ __forceinline__ void load_tile(uint8_t *dst, const CUtensorMap *map, 
 template<int D>
 __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_t k_lo)
 {
-    constexpr uint32_t idesc = idesc_bf16(BLK, BLK, 0, 0);
+    constexpr uint32_t idesc = idesc_16(BLK, BLK, 0, 0, ELEM_MMA_FORMAT);
     constexpr uint32_t hi = smem_desc_hi(1024);
 #pragma unroll
     for(int ks = 0; ks < D/16; ++ks)
@@ -170,7 +171,7 @@ template<int D, int HALF>
 __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo,
         bool accumulate)
 {
-    constexpr uint32_t idesc = idesc_bf16(BLK, D, 0, 1);
+    constexpr uint32_t idesc = idesc_16(BLK, D, 0, 1, ELEM_MMA_FORMAT);
     constexpr uint32_t hi = smem_desc_hi(1024);
 #pragma unroll
     for(int k4 = 0; k4 < BLK/32; ++k4)
@@ -204,8 +205,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
         const __grid_constant__ CUtensorMap tmap_a,
         int seq, int batch, int gsz, int kv_group, int kv_batch, float scale_log2,
-        const bf16 *__restrict__ mask, uint32_t *status, const uint8_t *__restrict__ cls_tab,
-        float *__restrict__ lse, bf16 *__restrict__ A)
+        const elem_t *__restrict__ mask, uint32_t *status, const uint8_t *__restrict__ cls_tab,
+        float *__restrict__ lse, elem_t *__restrict__ A)
 {
     extern __shared__ uint8_t smem_raw[];
     Smem<D> &sm = *reinterpret_cast<Smem<D> *>(
@@ -517,7 +518,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if(c == CLS_GENERIC)
             {
                 top_raw = -CUDART_INF_F;
-                const bf16 *mrow = mask + (size_t)(qb*BLK + r)*seq + (size_t)sm.list[it]*BLK;
+                const elem_t *mrow = mask + (size_t)(qb*BLK + r)*seq + (size_t)sm.list[it]*BLK;
 #pragma unroll
                 for(int g = 0; g < 16; ++g)
                 {
@@ -526,8 +527,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                     for(int e = 0; e < 8; ++e)
                     {
-                        const float bias = __uint_as_float(
-                                (e & 1) ? (w[e >> 1] & 0xFFFF0000u) : (w[e >> 1] << 16));
+                        const float bias = (e & 1) ? elem_hi(w[e >> 1]) : elem_lo(w[e >> 1]);
                         const float x = fmaf(__uint_as_float(s[g >> 2][8*(g & 3) + e]), scale_log2,
                                 bias*LOG2E_F);
                         s[g >> 2][8*(g & 3) + e] = __float_as_uint(x);
@@ -592,7 +592,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             m_used = m_new;
             const float neg_ref = m_used == -CUDART_INF_F ? 0.0f : -m_used;
             PROF_T(pt4);
-            // ---- P = exp2(x - m), row sum, bf16 pack, back into the S columns (in two
+            // ---- P = exp2(x - m), row sum, elem_t pack, back into the S columns (in two
             // rounds of 64 values to bound the registers), then one hand-over ---------
             const uint64_t mul2 = pack_f32x2(mul, mul), ref2 = pack_f32x2(neg_ref, neg_ref);
             uint64_t sum_a = 0ull, sum_b = 0ull;          // two packed chains = four sums
@@ -612,8 +612,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const float pa0 = ex2(xa0), pa1 = ex2(xa1), pb0 = ex2(xb0), pb1 = ex2(xb1);
                     sum_a = fadd2(sum_a, pack_f32x2(pa0, pa1));
                     sum_b = fadd2(sum_b, pack_f32x2(pb0, pb1));
-                    pk[j] = pack_bf16x2(pa0, pa1);
-                    pk[j + 1] = pack_bf16x2(pb0, pb1);
+                    pk[j] = pack_elem2(pa0, pa1);
+                    pk[j + 1] = pack_elem2(pb0, pb1);
                 }
                 tmem_st32(s_tm + 32*h, pk);
             }
@@ -702,7 +702,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                     for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        w[e2] = pack_bf16x2(__uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2])*inv,
+                        w[e2] = pack_elem2(__uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2])*inv,
                                 __uint_as_float(o[g8 >> 2][8*(g8 & 3) + 2*e2 + 1])*inv);
                     }
                     *reinterpret_cast<uint4 *>(prow + ((g8 ^ (lane & 7)) << 4)) =
@@ -732,7 +732,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             constexpr int LPR = D/8;                  // lanes (16-byte pieces) per row
             constexpr int RPI = 32/LPR;               // rows per warp instruction
             const int sub = lane/LPR, piece = lane % LPR;
-            bf16 *out = A + ((size_t)row_base + (size_t)qb*BLK + 32*(warp & 3))*D;
+            elem_t *out = A + ((size_t)row_base + (size_t)qb*BLK + 32*(warp & 3))*D;
 #pragma unroll
             for(int base = 0; base < 32; base += 8*RPI)
             {
@@ -764,11 +764,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                     for(int e2 = 0; e2 < 4; ++e2)
                     {
-                        outw[e2] = pack_bf16x2(
-                                wd[j]*__uint_as_float(pw[e2] << 16)
-                                        + ws[j]*__uint_as_float(gw[e2] << 16),
-                                wd[j]*__uint_as_float(pw[e2] & 0xFFFF0000u)
-                                        + ws[j]*__uint_as_float(gw[e2] & 0xFFFF0000u));
+                        outw[e2] = pack_elem2(
+                                wd[j]*elem_lo(pw[e2]) + ws[j]*elem_lo(gw[e2]),
+                                wd[j]*elem_hi(pw[e2]) + ws[j]*elem_hi(gw[e2]));
                     }
                     if(lv[j])
                     {
@@ -837,16 +835,17 @@ static std::atomic<uint32_t> g_wait_test_armed{0};
 
 template<int D>
 static int fwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index kv_batch,
-        const bf16 *K, const bf16 *Q,
-        const bf16 *mask, const bf16 *V, float *lse, bf16 *A, const FwdAux &aux)
+        const elem_t *K, const elem_t *Q,
+        const elem_t *mask, const elem_t *V, float *lse, elem_t *A, const FwdAux &aux)
 {
     using namespace fwd;
     CUtensorMap tq, tk, tv, ta;
     const uint64_t rows = (uint64_t)batch*seq;
     const uint64_t kv_rows = rows/(uint64_t)kv_group;
-    if(!make_tmap_bf16_sw128(&tq, Q, rows, D, BLK) || !make_tmap_bf16_sw128(&tk, K, kv_rows, D, BLK)
-            || !make_tmap_bf16_sw128(&tv, V, kv_rows, D, BLK)
-            || !make_tmap_bf16_sw128(&ta, A, rows, D, 32))
+    if(!make_tmap_16_sw128(&tq, Q, rows, D, BLK, ELEM_TMAP_TYPE)
+            || !make_tmap_16_sw128(&tk, K, kv_rows, D, BLK, ELEM_TMAP_TYPE)
+            || !make_tmap_16_sw128(&tv, V, kv_rows, D, BLK, ELEM_TMAP_TYPE)
+            || !make_tmap_16_sw128(&ta, A, rows, D, 32, ELEM_TMAP_TYPE))
     {
         return NNTILE_B200_E_LAUNCH;
     }
@@ -885,7 +884,7 @@ static int fwd_run(cudaStream_t s, Index seq, Index batch, Index kv_group, Index
     return launch_status();
 }
 
-int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *cls,
+int launch_mask_classify(cudaStream_t s, int seq, const elem_t *mask, uint8_t *cls,
         uint32_t *status)
 {
     const int nblk = seq/fwd::BLK;
@@ -893,8 +892,8 @@ int launch_mask_classify(cudaStream_t s, int seq, const bf16 *mask, uint8_t *cls
     return launch_status();
 }
 
-int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A, const FwdAux &aux,
+int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *mask, const elem_t *V, float *lse, elem_t *A, const FwdAux &aux,
         Index kv_group, Index kv_batch)
 {
     if(kv_group < 1 || kv_batch < 1 || batch % (kv_group*kv_batch) != 0 || !aux.status || !aux.cls)
@@ -906,10 +905,14 @@ int flash_fwd_sm100(cudaStream_t s, Index seq, Index head, Index batch, const bf
             : fwd_run<64>(s, seq, batch, kv_group, kv_batch, K, Q, mask, V, lse, A, aux);
 }
 
+} // inline namespace
 } // namespace nb200
 
-// Test support: arms the one-shot wait-timeout hook described in the header.
+#ifndef NB200_FP16
+// Test support: arms the one-shot wait-timeout hook described in the header (the
+// bfloat16 build's forward kernel).
 extern "C" void nntile_b200_test_arm_wait_timeout(void)
 {
     nb200::g_wait_test_armed.store(1u, std::memory_order_relaxed);
 }
+#endif

@@ -13,20 +13,21 @@
 #include "flash.cuh"
 
 namespace nb200 {
+inline namespace NB200_ELEM_NS {
 
 constexpr int GEN_MAX_EPL = 8;      // elements of a head vector per lane
 constexpr int GEN_WARPS = 4;
 
 // Load the lane's slice [lane*epl, lane*epl+epl) of a row of `head` elements.
 template<int EPL>
-__device__ __forceinline__ void load_slice(const bf16 *row, int head, int lane,
+__device__ __forceinline__ void load_slice(const elem_t *row, int head, int lane,
         float (&out)[EPL])
 {
 #pragma unroll
     for(int t = 0; t < EPL; ++t)
     {
         const int h = lane*EPL + t;
-        out[t] = h < head ? __bfloat162float(row[h]) : 0.0f;
+        out[t] = h < head ? elem_to_f(row[h]) : 0.0f;
     }
 }
 
@@ -46,9 +47,9 @@ __device__ __forceinline__ float dot_slice(const float (&a)[EPL], const float (&
 template<int EPL>
 __global__ void __launch_bounds__(GEN_WARPS*32)
 flash_fwd_generic_kernel(int seq, int head, Index rows, float scale,
-        const bf16 *__restrict__ K, const bf16 *__restrict__ Q,
-        const bf16 *__restrict__ mask, const bf16 *__restrict__ V,
-        float *__restrict__ lse, bf16 *__restrict__ A)
+        const elem_t *__restrict__ K, const elem_t *__restrict__ Q,
+        const elem_t *__restrict__ mask, const elem_t *__restrict__ V,
+        float *__restrict__ lse, elem_t *__restrict__ A)
 {
     const int lane = threadIdx.x & 31;
     const Index r = (Index)blockIdx.x*GEN_WARPS + (threadIdx.x >> 5);
@@ -58,7 +59,7 @@ flash_fwd_generic_kernel(int seq, int head, Index rows, float scale,
     }
     const Index b = r/seq;
     const int i = (int)(r - b*seq);
-    const bf16 *Kb = K + b*seq*head, *Vb = V + b*seq*head;
+    const elem_t *Kb = K + b*seq*head, *Vb = V + b*seq*head;
     float q[EPL], o[EPL], kv[EPL];
     load_slice<EPL>(Q + r*head, head, lane, q);
 #pragma unroll
@@ -67,10 +68,10 @@ flash_fwd_generic_kernel(int seq, int head, Index rows, float scale,
         o[t] = 0.0f;
     }
     float top = -CUDART_INF_F, sum = 0.0f;
-    const bf16 *mrow = mask + (Index)i*seq;
+    const elem_t *mrow = mask + (Index)i*seq;
     for(int j = 0; j < seq; ++j)
     {
-        const float bias = __bfloat162float(mrow[j]);
+        const float bias = elem_to_f(mrow[j]);
         if(bias == -CUDART_INF_F)
         {
             continue;                       // warp-uniform: the key is masked
@@ -128,17 +129,17 @@ flash_fwd_generic_kernel(int seq, int head, Index rows, float scale,
         {
             // the tile result is rounded to storage before the merge, as the
             // reference's scratch output is
-            const float part = __bfloat162float(__float2bfloat16_rn(o[t]*inv));
-            const float prev = __bfloat162float(A[r*head + h]);
-            A[r*head + h] = __float2bfloat16_rn(w_dst*prev + w_src*part);
+            const float part = elem_round((o[t]*inv));
+            const float prev = elem_to_f(A[r*head + h]);
+            A[r*head + h] = f_to_elem(w_dst*prev + w_src*part);
         }
     }
 }
 
 // ------------------------------------------------------------------- backward
 // delta[r] = sum_h A[r,h]*dA[r,h]
-__global__ void flash_bwd_delta_kernel(int head, Index rows, const bf16 *__restrict__ A,
-        const bf16 *__restrict__ dA, float *__restrict__ delta)
+__global__ void flash_bwd_delta_kernel(int head, Index rows, const elem_t *__restrict__ A,
+        const elem_t *__restrict__ dA, float *__restrict__ delta)
 {
     const int lane = threadIdx.x & 31;
     const Index r = (Index)blockIdx.x*(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -149,7 +150,7 @@ __global__ void flash_bwd_delta_kernel(int head, Index rows, const bf16 *__restr
     float acc = 0.0f;
     for(int h = lane; h < head; h += 32)
     {
-        acc = fmaf(__bfloat162float(A[r*head + h]), __bfloat162float(dA[r*head + h]), acc);
+        acc = fmaf(elem_to_f(A[r*head + h]), elem_to_f(dA[r*head + h]), acc);
     }
     acc = warp_sum(acc);
     if(lane == 0)
@@ -162,10 +163,10 @@ __global__ void flash_bwd_delta_kernel(int head, Index rows, const bf16 *__restr
 template<int EPL>
 __global__ void __launch_bounds__(GEN_WARPS*32)
 flash_bwd_dq_generic_kernel(int seq, int head, Index rows, float scale,
-        const bf16 *__restrict__ K, const bf16 *__restrict__ Q,
-        const bf16 *__restrict__ V, const bf16 *__restrict__ dA,
-        const bf16 *__restrict__ mask, const float *__restrict__ lse,
-        const float *__restrict__ delta, bf16 *__restrict__ dQ)
+        const elem_t *__restrict__ K, const elem_t *__restrict__ Q,
+        const elem_t *__restrict__ V, const elem_t *__restrict__ dA,
+        const elem_t *__restrict__ mask, const float *__restrict__ lse,
+        const float *__restrict__ delta, elem_t *__restrict__ dQ)
 {
     const int lane = threadIdx.x & 31;
     const Index r = (Index)blockIdx.x*GEN_WARPS + (threadIdx.x >> 5);
@@ -175,7 +176,7 @@ flash_bwd_dq_generic_kernel(int seq, int head, Index rows, float scale,
     }
     const Index b = r/seq;
     const int i = (int)(r - b*seq);
-    const bf16 *Kb = K + b*seq*head, *Vb = V + b*seq*head;
+    const elem_t *Kb = K + b*seq*head, *Vb = V + b*seq*head;
     float q[EPL], g[EPL], acc[EPL], kk[EPL], vv[EPL];
     load_slice<EPL>(Q + r*head, head, lane, q);
     load_slice<EPL>(dA + r*head, head, lane, g);
@@ -185,10 +186,10 @@ flash_bwd_dq_generic_kernel(int seq, int head, Index rows, float scale,
         acc[t] = 0.0f;
     }
     const float row_lse = lse[r], row_delta = delta[r];
-    const bf16 *mrow = mask + (Index)i*seq;
+    const elem_t *mrow = mask + (Index)i*seq;
     for(int j = 0; j < seq; ++j)
     {
-        const float bias = __bfloat162float(mrow[j]);
+        const float bias = elem_to_f(mrow[j]);
         if(bias == -CUDART_INF_F)
         {
             continue;
@@ -211,8 +212,8 @@ flash_bwd_dq_generic_kernel(int seq, int head, Index rows, float scale,
         const int h = lane*EPL + t;
         if(h < head)
         {
-            const float part = __bfloat162float(__float2bfloat16_rn(acc[t]));
-            dQ[r*head + h] = __float2bfloat16_rn(part + __bfloat162float(dQ[r*head + h]));
+            const float part = elem_round((acc[t]));
+            dQ[r*head + h] = f_to_elem(part + elem_to_f(dQ[r*head + h]));
         }
     }
 }
@@ -221,10 +222,10 @@ flash_bwd_dq_generic_kernel(int seq, int head, Index rows, float scale,
 template<int EPL>
 __global__ void __launch_bounds__(GEN_WARPS*32)
 flash_bwd_dkv_generic_kernel(int seq, int head, Index rows, float scale,
-        const bf16 *__restrict__ K, const bf16 *__restrict__ Q,
-        const bf16 *__restrict__ V, const bf16 *__restrict__ dA,
-        const bf16 *__restrict__ mask, const float *__restrict__ lse,
-        const float *__restrict__ delta, bf16 *__restrict__ dK, bf16 *__restrict__ dV)
+        const elem_t *__restrict__ K, const elem_t *__restrict__ Q,
+        const elem_t *__restrict__ V, const elem_t *__restrict__ dA,
+        const elem_t *__restrict__ mask, const float *__restrict__ lse,
+        const float *__restrict__ delta, elem_t *__restrict__ dK, elem_t *__restrict__ dV)
 {
     const int lane = threadIdx.x & 31;
     const Index r = (Index)blockIdx.x*GEN_WARPS + (threadIdx.x >> 5);
@@ -234,7 +235,7 @@ flash_bwd_dkv_generic_kernel(int seq, int head, Index rows, float scale,
     }
     const Index b = r/seq;
     const int j = (int)(r - b*seq);
-    const bf16 *Qb = Q + b*seq*head, *Gb = dA + b*seq*head;
+    const elem_t *Qb = Q + b*seq*head, *Gb = dA + b*seq*head;
     float kk[EPL], vv[EPL], gk[EPL], gv[EPL], qq[EPL], gg[EPL];
     load_slice<EPL>(K + r*head, head, lane, kk);
     load_slice<EPL>(V + r*head, head, lane, vv);
@@ -246,7 +247,7 @@ flash_bwd_dkv_generic_kernel(int seq, int head, Index rows, float scale,
     }
     for(int i = 0; i < seq; ++i)
     {
-        const float bias = __bfloat162float(mask[(Index)i*seq + j]);
+        const float bias = elem_to_f(mask[(Index)i*seq + j]);
         if(bias == -CUDART_INF_F)
         {
             continue;
@@ -270,17 +271,17 @@ flash_bwd_dkv_generic_kernel(int seq, int head, Index rows, float scale,
         const int h = lane*EPL + t;
         if(h < head)
         {
-            const float pk = __bfloat162float(__float2bfloat16_rn(gk[t]));
-            const float pv = __bfloat162float(__float2bfloat16_rn(gv[t]));
-            dK[r*head + h] = __float2bfloat16_rn(pk + __bfloat162float(dK[r*head + h]));
-            dV[r*head + h] = __float2bfloat16_rn(pv + __bfloat162float(dV[r*head + h]));
+            const float pk = elem_round((gk[t]));
+            const float pv = elem_round((gv[t]));
+            dK[r*head + h] = f_to_elem(pk + elem_to_f(dK[r*head + h]));
+            dV[r*head + h] = f_to_elem(pv + elem_to_f(dV[r*head + h]));
         }
     }
 }
 
 template<int EPL>
 static int fwd_launch(cudaStream_t s, int seq, int head, Index rows, float scale,
-        const bf16 *K, const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A)
+        const elem_t *K, const elem_t *Q, const elem_t *mask, const elem_t *V, float *lse, elem_t *A)
 {
     const unsigned blocks = (unsigned)((rows + GEN_WARPS - 1)/GEN_WARPS);
     flash_fwd_generic_kernel<EPL><<<blocks, GEN_WARPS*32, 0, s>>>(seq, head, rows, scale,
@@ -288,8 +289,8 @@ static int fwd_launch(cudaStream_t s, int seq, int head, Index rows, float scale
     return launch_status();
 }
 
-int flash_fwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *mask, const bf16 *V, float *lse, bf16 *A)
+int flash_fwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *mask, const elem_t *V, float *lse, elem_t *A)
 {
     const Index rows = seq*batch;
     const float scale = 1.0f/sqrtf((float)head);
@@ -307,8 +308,8 @@ int flash_fwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const 
 
 template<int EPL>
 static int bwd_launch(cudaStream_t s, int seq, int head, Index rows, float scale,
-        const bf16 *K, const bf16 *Q, const bf16 *V, const bf16 *dA, const bf16 *mask,
-        const float *lse, const float *delta, bf16 *dK, bf16 *dQ, bf16 *dV)
+        const elem_t *K, const elem_t *Q, const elem_t *V, const elem_t *dA, const elem_t *mask,
+        const float *lse, const float *delta, elem_t *dK, elem_t *dQ, elem_t *dV)
 {
     const unsigned blocks = (unsigned)((rows + GEN_WARPS - 1)/GEN_WARPS);
     flash_bwd_dq_generic_kernel<EPL><<<blocks, GEN_WARPS*32, 0, s>>>(seq, head, rows,
@@ -318,16 +319,16 @@ static int bwd_launch(cudaStream_t s, int seq, int head, Index rows, float scale
     return launch_status(2);
 }
 
-int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const bf16 *A, const bf16 *dA,
+int flash_bwd_delta(cudaStream_t s, Index head, Index rows, const elem_t *A, const elem_t *dA,
         float *delta)
 {
     flash_bwd_delta_kernel<<<(unsigned)((rows + 7)/8), 256, 0, s>>>((int)head, rows, A, dA, delta);
     return launch_status();
 }
 
-int flash_bwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const bf16 *K,
-        const bf16 *Q, const bf16 *V, const bf16 *A, const bf16 *dA, const bf16 *mask,
-        const float *lse, float *delta, bf16 *dK, bf16 *dQ, bf16 *dV)
+int flash_bwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const elem_t *K,
+        const elem_t *Q, const elem_t *V, const elem_t *A, const elem_t *dA, const elem_t *mask,
+        const float *lse, float *delta, elem_t *dK, elem_t *dQ, elem_t *dV)
 {
     const Index rows = seq*batch;
     const float scale = 1.0f/sqrtf((float)head);
@@ -348,4 +349,5 @@ int flash_bwd_generic(cudaStream_t s, Index seq, Index head, Index batch, const 
     }
 }
 
+} // inline namespace
 } // namespace nb200

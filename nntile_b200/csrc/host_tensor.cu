@@ -14,7 +14,7 @@
 //   forward   tasks of one Q tile run in K/V-tile order on one helper stream (they
 //             merge into the same (lse, A)); different Q tiles run side by side.
 //   backward  tasks that add into the same dK/dV tile run in Q-tile order on one
-//             helper stream, so the bf16 "+=" into dK, dV happens in the reference's
+//             helper stream, so the elem_t "+=" into dK, dV happens in the reference's
 //             order; dQ of a Q tile is summed in fp32 over all its K/V tiles
 //             (red.add, any order) and rounded into dQ once, after the join.
 // Work shared by the tasks of a call is done once: every distinct mask buffer is
@@ -28,6 +28,7 @@
 #include "per_device.hh"
 
 namespace nb200 {
+inline namespace NB200_ELEM_NS {
 
 struct Grid5
 {
@@ -228,7 +229,7 @@ static int classify_masks(cudaStream_t s, const Grid5 &g, const void *const *mas
         {
             if(!aligned16(m)) return NNTILE_B200_E_ALIGN;
             slot = cls_base + (size_t)p*cls_slot;
-            const int st = launch_mask_classify(s, (int)g.tile[1], (const bf16 *)m, slot, nullptr);
+            const int st = launch_mask_classify(s, (int)g.tile[1], (const elem_t *)m, slot, nullptr);
             if(st != NNTILE_B200_OK) return st;
             seen.emplace_back(m, slot);
         }
@@ -312,9 +313,9 @@ static int tensor_fwd(cudaStream_t stream, const int64_t *shape, const int64_t *
                 }
                 const FwdAux aux = {reinterpret_cast<uint32_t *>(base),
                         slot_of[(size_t)(ki + qi*nseq)], false};
-                st = flash_fwd_sm100(s, seq_q, g.shape[0], batch, (const bf16 *)K_tiles[kv],
-                        (const bf16 *)Q_tiles[a], (const bf16 *)m, (const bf16 *)V_tiles[kv],
-                        lse_tiles[a], (bf16 *)A_tiles[a], aux, gqa ? gt : 1, gqa ? bt : batch);
+                st = flash_fwd_sm100(s, seq_q, g.shape[0], batch, (const elem_t *)K_tiles[kv],
+                        (const elem_t *)Q_tiles[a], (const elem_t *)m, (const elem_t *)V_tiles[kv],
+                        lse_tiles[a], (elem_t *)A_tiles[a], aux, gqa ? gt : 1, gqa ? bt : batch);
             }
             else
             {
@@ -425,10 +426,10 @@ static int tensor_bwd(cudaStream_t stream, const int64_t *shape, const int64_t *
             return NNTILE_B200_E_ALIGN;
         }
         // K, V, mask are not touched by this phase
-        st = flash_bwd_sm100(stream, seq_q, D, batch, (const bf16 *)Q_tiles[a],
-                (const bf16 *)Q_tiles[a], (const bf16 *)Q_tiles[a], (const bf16 *)A_tiles[a],
-                (const bf16 *)dA_tiles[a], (const bf16 *)Q_tiles[a], lse_tiles[a], x,
-                (bf16 *)dQ_tiles[a], (bf16 *)dQ_tiles[a], (bf16 *)dQ_tiles[a], 1, batch);
+        st = flash_bwd_sm100(stream, seq_q, D, batch, (const elem_t *)Q_tiles[a],
+                (const elem_t *)Q_tiles[a], (const elem_t *)Q_tiles[a], (const elem_t *)A_tiles[a],
+                (const elem_t *)dA_tiles[a], (const elem_t *)Q_tiles[a], lse_tiles[a], x,
+                (elem_t *)dQ_tiles[a], (elem_t *)dQ_tiles[a], (elem_t *)dQ_tiles[a], 1, batch);
         if(st != NNTILE_B200_OK) return st;
     }
     {
@@ -460,11 +461,11 @@ static int tensor_bwd(cudaStream_t stream, const int64_t *shape, const int64_t *
                 BwdAux x = aux[(size_t)a];
                 x.cls = slot_of[(size_t)(ki + qi*nseq)];
                 x.phases = BWD_MAIN;
-                st = flash_bwd_sm100(fj.lane(kv), seq_q, D, batch, (const bf16 *)K_tiles[kv],
-                        (const bf16 *)Q_tiles[a], (const bf16 *)V_tiles[kv],
-                        (const bf16 *)A_tiles[a], (const bf16 *)dA_tiles[a], (const bf16 *)m,
-                        lse_tiles[a], x, (bf16 *)dK_tiles[kv], (bf16 *)dQ_tiles[a],
-                        (bf16 *)dV_tiles[kv], gqa ? gt : 1, gqa ? bt : batch);
+                st = flash_bwd_sm100(fj.lane(kv), seq_q, D, batch, (const elem_t *)K_tiles[kv],
+                        (const elem_t *)Q_tiles[a], (const elem_t *)V_tiles[kv],
+                        (const elem_t *)A_tiles[a], (const elem_t *)dA_tiles[a], (const elem_t *)m,
+                        lse_tiles[a], x, (elem_t *)dK_tiles[kv], (elem_t *)dQ_tiles[a],
+                        (elem_t *)dV_tiles[kv], gqa ? gt : 1, gqa ? bt : batch);
                 if(st != NNTILE_B200_OK) return st;
             }
         }
@@ -479,20 +480,21 @@ static int tensor_bwd(cudaStream_t stream, const int64_t *shape, const int64_t *
         const Index batch = extent(g, 2, idx[2])*extent(g, 3, idx[3])*extent(g, 4, idx[4]);
         BwdAux x = aux[(size_t)a];
         x.phases = BWD_FINISH;
-        st = flash_bwd_sm100(stream, seq_q, D, batch, (const bf16 *)Q_tiles[a],
-                (const bf16 *)Q_tiles[a], (const bf16 *)Q_tiles[a], (const bf16 *)A_tiles[a],
-                (const bf16 *)dA_tiles[a], (const bf16 *)Q_tiles[a], lse_tiles[a], x,
-                (bf16 *)dQ_tiles[a], (bf16 *)dQ_tiles[a], (bf16 *)dQ_tiles[a], 1, batch);
+        st = flash_bwd_sm100(stream, seq_q, D, batch, (const elem_t *)Q_tiles[a],
+                (const elem_t *)Q_tiles[a], (const elem_t *)Q_tiles[a], (const elem_t *)A_tiles[a],
+                (const elem_t *)dA_tiles[a], (const elem_t *)Q_tiles[a], lse_tiles[a], x,
+                (elem_t *)dQ_tiles[a], (elem_t *)dQ_tiles[a], (elem_t *)dQ_tiles[a], 1, batch);
         if(st != NNTILE_B200_OK) return st;
     }
     return NNTILE_B200_OK;
 }
 
+} // inline namespace
 } // namespace nb200
 
 using namespace nb200;
 
-extern "C" int nntile_b200_tensor_flash_sdpa_fwd_bf16(nntile_b200_stream_t stream,
+extern "C" int NB200_SFX(nntile_b200_tensor_flash_sdpa_fwd)(nntile_b200_stream_t stream,
         const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
         const void *const *Q_tiles, const void *const *mask_tiles, float *const *lse_tiles,
         const void *const *V_tiles, void *const *A_tiles, void *scratch,
@@ -502,7 +504,7 @@ extern "C" int nntile_b200_tensor_flash_sdpa_fwd_bf16(nntile_b200_stream_t strea
             lse_tiles, V_tiles, A_tiles, scratch, scratch_bytes, false);
 }
 
-extern "C" int nntile_b200_tensor_flash_sdpa_bwd_bf16(nntile_b200_stream_t stream,
+extern "C" int NB200_SFX(nntile_b200_tensor_flash_sdpa_bwd)(nntile_b200_stream_t stream,
         const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
         const void *const *Q_tiles, const void *const *V_tiles, const void *const *A_tiles,
         const void *const *dA_tiles, const void *const *mask_tiles,
@@ -514,7 +516,7 @@ extern "C" int nntile_b200_tensor_flash_sdpa_bwd_bf16(nntile_b200_stream_t strea
             scratch_bytes, false);
 }
 
-extern "C" int nntile_b200_tensor_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t stream,
+extern "C" int NB200_SFX(nntile_b200_tensor_flash_sdpa_fwd_gqa)(nntile_b200_stream_t stream,
         const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
         const void *const *Q_tiles, const void *const *mask_tiles, float *const *lse_tiles,
         const void *const *V_tiles, void *const *A_tiles, void *scratch,
@@ -524,7 +526,7 @@ extern "C" int nntile_b200_tensor_flash_sdpa_fwd_gqa_bf16(nntile_b200_stream_t s
             lse_tiles, V_tiles, A_tiles, scratch, scratch_bytes, true);
 }
 
-extern "C" int nntile_b200_tensor_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t stream,
+extern "C" int NB200_SFX(nntile_b200_tensor_flash_sdpa_bwd_gqa)(nntile_b200_stream_t stream,
         const int64_t *shape, const int64_t *basetile, const void *const *K_tiles,
         const void *const *Q_tiles, const void *const *V_tiles, const void *const *A_tiles,
         const void *const *dA_tiles, const void *const *mask_tiles,
@@ -536,6 +538,7 @@ extern "C" int nntile_b200_tensor_flash_sdpa_bwd_gqa_bf16(nntile_b200_stream_t s
             scratch_bytes, true);
 }
 
+#ifndef NB200_FP16
 extern "C" size_t nntile_b200_tensor_flash_sdpa_scratch_bytes(const int64_t *shape,
         const int64_t *basetile)
 {
@@ -543,3 +546,4 @@ extern "C" size_t nntile_b200_tensor_flash_sdpa_scratch_bytes(const int64_t *sha
     if(!shape || !basetile || !make_grid(shape, basetile, g)) return 0;
     return make_layout(g).total;
 }
+#endif // NB200_FP16

@@ -261,11 +261,18 @@ __device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo, uint32_t hi)
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulate:
 //   bits 4-5 D format (1 = f32)   bits 7-9 A format (1 = bf16)   bits 10-12 B format
 //   bit 15 A major (0 = K, 1 = MN)   bit 16 B major   bits 17-22 N>>3   bits 24-28 M>>4
-__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major)
+// `fmt` is the format of both operands: 0 = f16, 1 = bf16.
+__host__ __device__ constexpr uint32_t idesc_16(int M, int N, int a_mn_major, int b_mn_major,
+        uint32_t fmt)
 {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15)
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn_major << 15)
             | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17)
             | ((uint32_t)(M >> 4) << 24);
+}
+
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major)
+{
+    return idesc_16(M, N, a_mn_major, b_mn_major, 1u);
 }
 
 // ------------------------------------------------------------------------ MMA
@@ -495,11 +502,11 @@ inline EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
-// Row-major bf16 matrix [rows][cols] (cols contiguous) cut into boxes of
-// box_rows x 64 columns (128 bytes), written to shared memory with the 128-byte
+// Row-major matrix of 16-bit elements [rows][cols] (cols contiguous) cut into boxes
+// of box_rows x 64 columns (128 bytes), written to shared memory with the 128-byte
 // swizzle that the MMA descriptors above expect.
-inline bool make_tmap_bf16_sw128(CUtensorMap *map, const void *base, uint64_t rows,
-        uint64_t cols, uint32_t box_rows)
+inline bool make_tmap_16_sw128(CUtensorMap *map, const void *base, uint64_t rows,
+        uint64_t cols, uint32_t box_rows, CUtensorMapDataType type)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if(!fn)
@@ -510,7 +517,7 @@ inline bool make_tmap_bf16_sw128(CUtensorMap *map, const void *base, uint64_t ro
     cuuint64_t strides[1] = {cols*2};
     cuuint32_t box[2] = {64, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+    return fn(map, type, 2, const_cast<void *>(base), dims,
             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
             == CUDA_SUCCESS;

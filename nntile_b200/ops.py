@@ -38,6 +38,15 @@ def _sfx(t) -> str:
     raise TypeError(f"unsupported dtype {t.dtype}")
 
 
+def _sfx16(t) -> str:
+    """Suffix of the fused-pair entry points: bfloat16 or IEEE half."""
+    if t.dtype == torch.bfloat16:
+        return "bf16"
+    if t.dtype == torch.float16:
+        return "fp16"
+    raise TypeError(f"the fused path takes bfloat16 or float16, not {t.dtype}")
+
+
 def _call(name, *args):
     fn = getattr(_lib.load(), name)
     _lib.check(name, fn(*args))
@@ -140,14 +149,14 @@ def flash_sdpa_read_status(scratch) -> int:
 
 def flash_sdpa_fwd(seq, head, batch, K, Q, mask, scratch_lse, V, scratch_A, lse, A):
     """Pointer order of flash_sdpa_fwd_cudnn::execute_graph."""
-    _call("nntile_b200_flash_sdpa_fwd_bf16", _stream(), seq, head, batch, _ptr(K), _ptr(Q),
+    _call(f"nntile_b200_flash_sdpa_fwd_{_sfx16(Q)}", _stream(), seq, head, batch, _ptr(K), _ptr(Q),
           _ptr(mask), _ptr(scratch_lse), _ptr(V), _ptr(scratch_A), _ptr(lse), _ptr(A))
 
 
 def flash_sdpa_bwd(seq, head, batch, K, Q, V, A, dA, mask, lse, scratch_dK, scratch_dQ,
                    scratch_dV, dK, dQ, dV):
     """Pointer order of flash_sdpa_bwd_cudnn::execute_graph."""
-    _call("nntile_b200_flash_sdpa_bwd_bf16", _stream(), seq, head, batch, _ptr(K), _ptr(Q),
+    _call(f"nntile_b200_flash_sdpa_bwd_{_sfx16(Q)}", _stream(), seq, head, batch, _ptr(K), _ptr(Q),
           _ptr(V), _ptr(A), _ptr(dA), _ptr(mask), _ptr(lse), _ptr(scratch_dK),
           _ptr(scratch_dQ), _ptr(scratch_dV), _ptr(dK), _ptr(dQ), _ptr(dV))
 
@@ -159,14 +168,14 @@ def flash_sdpa_gqa_scratch_bytes(seq, head, batch, group, kv_heads) -> int:
 
 def flash_sdpa_fwd_gqa(seq, head, batch, group, kv_heads, K, Q, mask, V, lse, A, scratch):
     """K, V un-replicated [head, seq, batch, kv_heads]; Q, A with the group index."""
-    _call("nntile_b200_flash_sdpa_fwd_gqa_bf16", _stream(), seq, head, batch, group, kv_heads,
+    _call(f"nntile_b200_flash_sdpa_fwd_gqa_{_sfx16(Q)}", _stream(), seq, head, batch, group, kv_heads,
           _ptr(K), _ptr(Q), _ptr(mask), _ptr(V), _ptr(lse), _ptr(A), _ptr(scratch),
           scratch.numel()*scratch.element_size())
 
 
 def flash_sdpa_bwd_gqa(seq, head, batch, group, kv_heads, K, Q, V, A, dA, mask, lse, dK, dQ, dV,
                        scratch):
-    _call("nntile_b200_flash_sdpa_bwd_gqa_bf16", _stream(), seq, head, batch, group, kv_heads,
+    _call(f"nntile_b200_flash_sdpa_bwd_gqa_{_sfx16(Q)}", _stream(), seq, head, batch, group, kv_heads,
           _ptr(K), _ptr(Q), _ptr(V), _ptr(A), _ptr(dA), _ptr(mask), _ptr(lse), _ptr(dK),
           _ptr(dQ), _ptr(dV), _ptr(scratch), scratch.numel()*scratch.element_size())
 

@@ -25,7 +25,7 @@ from . import _lib, ops
 
 
 def from_fortran(arr: np.ndarray, device="cuda") -> torch.Tensor:
-    """numpy Fortran array (float32, or uint16 = bf16 bits) -> torch buffer."""
+    """numpy Fortran array (float32, float16, or uint16 = bf16 bits) -> torch buffer."""
     a = np.asfortranarray(arr)
     if a.dtype == np.uint16:
         return torch.from_numpy(a.T.view(np.int16).copy()).view(torch.bfloat16).to(device)
@@ -116,8 +116,7 @@ def flash_sdpa_fwd_async(K, Q, mask, lse, V, A, seq_tile=None, batch_tile=None, 
     tQ, tA = TiledBuffer(Q, base5), TiledBuffer(A, base5)
     tM = TiledBuffer(mask, (seq_tile, seq_tile))
     tL = TiledBuffer(lse, (seq_tile,) + bt)
-    name = "nntile_b200_tensor_flash_sdpa_fwd_gqa_bf16" if gqa \
-        else "nntile_b200_tensor_flash_sdpa_fwd_bf16"
+    name = f"nntile_b200_tensor_flash_sdpa_fwd{'_gqa' if gqa else ''}_{ops._sfx16(Q)}"
     _tensor_call(name, (D, S, B, G, H), base5, [tK, tQ, tM, tL, tV, tA], scratch_out)
     A.copy_(tA.gather())
     lse.copy_(tL.gather())
@@ -137,8 +136,7 @@ def flash_sdpa_bwd_async(K, Q, V, A, dA, mask, lse, dK, dQ, dV, seq_tile=None,
     tQ, tA, tdA, tdQ = (TiledBuffer(x, base5) for x in (Q, A, dA, dQ))
     tM = TiledBuffer(mask, (seq_tile, seq_tile))
     tL = TiledBuffer(lse, (seq_tile,) + bt)
-    name = "nntile_b200_tensor_flash_sdpa_bwd_gqa_bf16" if gqa \
-        else "nntile_b200_tensor_flash_sdpa_bwd_bf16"
+    name = f"nntile_b200_tensor_flash_sdpa_bwd{'_gqa' if gqa else ''}_{ops._sfx16(Q)}"
     _tensor_call(name, (D, S, B, G, H), base5, [tK, tQ, tV, tA, tdA, tM, tL, tdK, tdQ, tdV],
                  scratch_out)
     dK.copy_(tdK.gather())
@@ -273,8 +271,8 @@ class Sdpa:
         dev, dt = q.device, q.dtype
         self.y = torch.zeros_like(q)
         if flash_attention:
-            if dt != torch.bfloat16:
-                raise TypeError("the fused path takes bf16 only (fp32 is rejected by the "
+            if dt not in (torch.bfloat16, torch.float16):
+                raise TypeError("the fused path takes bf16 or fp16 (fp32 is rejected by the "
                                 "reference as well, flash_sdpa_fwd_cudnn/cuda.cc:60-63)")
             self.flash_logsumexp = torch.empty((H, G, B, S), dtype=torch.float32, device=dev)
             if mask is None:

@@ -73,7 +73,8 @@ public:
 
 using flash_sdpa_bwd_cudnn_pack_t = OperationPack<
     FlashSdpaBwdCudnn,
-    std::tuple<nntile::bf16_t>
+    std::tuple<nntile::bf16_t>,
+    std::tuple<nntile::fp16_t>
 >;
 
 extern flash_sdpa_bwd_cudnn_pack_t flash_sdpa_bwd_cudnn;

@@ -75,10 +75,11 @@ public:
     );
 };
 
-//! The reference instantiates bf16 and fp16; the sm_100a kernels are bf16
+//! bf16 and fp16, as in the reference
 using flash_sdpa_fwd_cudnn_pack_t = OperationPack<
     FlashSdpaFwdCudnn,
-    std::tuple<nntile::bf16_t>
+    std::tuple<nntile::bf16_t>,
+    std::tuple<nntile::fp16_t>
 >;
 
 extern flash_sdpa_fwd_cudnn_pack_t flash_sdpa_fwd_cudnn;

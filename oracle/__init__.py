@@ -16,7 +16,8 @@ On top of them this module restates the StarPU-bound host logic that cannot be
 compiled here: the (m, n, k) derivations of the tile layer, the tile loops of
 the tensor layer, and the order of operations of ``nntile.layer.Sdpa``.
 
-Arrays are numpy, Fortran order.  dtype float32 is fp32; dtype uint16 holds
+Arrays are numpy, Fortran order.  dtype float32 is fp32; dtype float16 is IEEE half
+(the fused pair only); dtype uint16 holds
 bfloat16 bit patterns (round to nearest even, the reference's CUDA build).
 """
 from __future__ import annotations
@@ -89,10 +90,14 @@ def _sfx(a: np.ndarray) -> str:
         return "f32"
     if a.dtype == np.uint16:
         return "bf16"
+    if a.dtype == np.float16:
+        return "f16"
     raise TypeError(f"oracle: unsupported dtype {a.dtype}")
 
 
 def _fn(backend: str, name: str, sfx: str):
+    if backend == "ref" and sfx == "f16":
+        backend = "port"      # oracle/_ref carries the fp32 and bf16 instantiations
     if backend == "ref":
         if ref is None:
             raise RuntimeError("oracle: _ref library not built")
@@ -123,12 +128,14 @@ def from_bf16(u) -> np.ndarray:
 
 
 def as_f32(a) -> np.ndarray:
-    return from_bf16(a) if a.dtype == np.uint16 else np.asarray(a, np.float32)
+    return from_bf16(a) if a.dtype == np.uint16 else np.asfortranarray(a, dtype=np.float32)
 
 
 def cast(x_f32, like_dtype) -> np.ndarray:
     if np.dtype(like_dtype) == np.uint16:
         return to_bf16(x_f32)
+    if np.dtype(like_dtype) == np.float16:
+        return np.asfortranarray(x_f32, dtype=np.float16)      # round to nearest even
     return np.asfortranarray(x_f32, dtype=np.float32)
 
 

@@ -60,6 +60,18 @@ static inline uint16_t f32_to_bf16(float f)
 #undef ST
 #undef FN
 
+/* IEEE half storage (the reference's fp16_t): conversions are the compiler's,
+ * round to nearest even. */
+#define T _Float16
+#define LD(x) ((float)(x))
+#define ST(x) ((_Float16)(x))
+#define FN(name) name##_f16
+#include "ops_impl.inc"
+#undef T
+#undef LD
+#undef ST
+#undef FN
+
 /* Conversions exported for the Python side of the test-suite. */
 void orc_f32_to_bf16(int64_t n, const float *src, uint16_t *dst)
 {

@@ -19,5 +19,9 @@ int main()
     if(nntile_b200::last_status() != NNTILE_B200_E_BADARG) return 3;
     kernel::flash_sdpa_fwd::cuda<bf16_t>(s, 128, 64, 1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
     kernel::flash_sdpa_bwd::cuda<bf16_t>(s, 128, 64, 1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
-    return nntile_b200::last_status() == NNTILE_B200_E_BADARG ? 0 : 1;
+    if(nntile_b200::last_status() != NNTILE_B200_E_BADARG) return 1;
+    kernel::flash_sdpa_fwd::cuda<fp16_t>(s, 128, 64, 1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+    if(nntile_b200::last_status() != NNTILE_B200_E_BADARG) return 4;
+    kernel::flash_sdpa_bwd::cuda<fp16_t>(s, 128, 64, 1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+    return nntile_b200::last_status() == NNTILE_B200_E_BADARG ? 0 : 5;
 }

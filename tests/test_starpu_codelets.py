@@ -37,11 +37,11 @@ def chk():
         pytest.skip("no reference checkout here and no prebuilt codelet check library")
     lib = ctypes.CDLL(path)
     vp, i64 = ctypes.c_void_p, ctypes.c_int64
-    lib.codelet_check_fwd.argtypes = [vp, i64, i64, i64] + [vp]*8
-    lib.codelet_check_bwd.argtypes = [vp, i64, i64, i64] + [vp]*13
+    lib.codelet_check_fwd.argtypes = [vp, ctypes.c_int, i64, i64, i64] + [vp]*8
+    lib.codelet_check_bwd.argtypes = [vp, ctypes.c_int, i64, i64, i64] + [vp]*13
     lib.codelet_check_footprint.argtypes = [ctypes.c_int, i64, i64, i64]
     lib.codelet_check_footprint.restype = ctypes.c_uint32
-    lib.codelet_check_name.argtypes = [ctypes.c_int]
+    lib.codelet_check_name.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.codelet_check_name.restype = ctypes.c_char_p
     lib.starpu_fake_tasks_run.restype = ctypes.c_int
     return lib
@@ -49,8 +49,10 @@ def chk():
 
 def test_codelets_keep_the_reference_names_and_footprints(chk):
     # src/starpu/flash_sdpa_fwd_cudnn.cc:42 / flash_sdpa_bwd_cudnn.cc:37 + type postfix
-    assert chk.codelet_check_name(1) == b"nntile_flash_sdpa_fwd_cudnn_bf16"
-    assert chk.codelet_check_name(0) == b"nntile_flash_sdpa_bwd_cudnn_bf16"
+    assert chk.codelet_check_name(1, 0) == b"nntile_flash_sdpa_fwd_cudnn_bf16"
+    assert chk.codelet_check_name(0, 0) == b"nntile_flash_sdpa_bwd_cudnn_bf16"
+    assert chk.codelet_check_name(1, 1) == b"nntile_flash_sdpa_fwd_cudnn_fp16"
+    assert chk.codelet_check_name(0, 1) == b"nntile_flash_sdpa_bwd_cudnn_fp16"
     a = chk.codelet_check_footprint(1, 1024, 64, 96)
     assert a == chk.codelet_check_footprint(1, 1024, 64, 96)
     assert a != chk.codelet_check_footprint(1, 2048, 64, 96)
@@ -62,24 +64,28 @@ def test_a_submitted_task_reaches_the_library(chk, capfd):
     refuses before any launch and the worker body reports it on stderr."""
     null = ctypes.c_void_p(0)
     before = chk.starpu_fake_tasks_run()
-    assert chk.codelet_check_fwd(null, 128, 64, 1, *([null]*8)) == 8
-    assert chk.codelet_check_bwd(null, 128, 64, 1, *([null]*13)) == 13
-    assert chk.starpu_fake_tasks_run() == before + 2
+    for fp16 in (0, 1):
+        assert chk.codelet_check_fwd(null, fp16, 128, 64, 1, *([null]*8)) == 8
+        assert chk.codelet_check_bwd(null, fp16, 128, 64, 1, *([null]*13)) == 13
+    assert chk.starpu_fake_tasks_run() == before + 4
     err = capfd.readouterr().err
-    assert "nntile_b200_flash_sdpa_fwd_bf16" in err and "nntile_b200_flash_sdpa_bwd_bf16" in err
+    assert err.count("nntile_b200_flash_sdpa_fwd: bad argument") == 2
+    assert err.count("nntile_b200_flash_sdpa_bwd: bad argument") == 2
 
 
 @pytest.mark.gpu
-def test_codelet_task_equals_direct_call(chk):
+@pytest.mark.parametrize("fp16", [0, 1])
+def test_codelet_task_equals_direct_call(chk, fp16):
     import torch
 
     from nntile_b200 import ops
     torch.manual_seed(5)
     seq, head, batch = 256, 128, 3
-    mk = lambda: torch.randn((batch, seq, head), device="cuda").to(torch.bfloat16)
+    dt = torch.float16 if fp16 else torch.bfloat16
+    mk = lambda: torch.randn((batch, seq, head), device="cuda").to(dt)
     Q, K, V, dA = mk(), mk(), mk(), mk()
     qi = torch.arange(seq, device="cuda")
-    mask = torch.where(qi[None, :] > qi[:, None], float("-inf"), 0.0).to(torch.bfloat16)
+    mask = torch.where(qi[None, :] > qi[:, None], float("-inf"), 0.0).to(dt)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     res = []
@@ -90,9 +96,9 @@ def test_codelet_task_equals_direct_call(chk):
             torch.empty_like(Q)
         dK, dQ, dV = (torch.zeros_like(Q) for _ in range(3))
         if via_codelet:
-            assert chk.codelet_check_fwd(stream, seq, head, batch, p(K), p(Q), p(mask), p(lse),
+            assert chk.codelet_check_fwd(stream, fp16, seq, head, batch, p(K), p(Q), p(mask), p(lse),
                                          p(V), p(A), p(s_lse), p(s1)) == 8
-            assert chk.codelet_check_bwd(stream, seq, head, batch, p(K), p(Q), p(V), p(A), p(dA),
+            assert chk.codelet_check_bwd(stream, fp16, seq, head, batch, p(K), p(Q), p(V), p(A), p(dA),
                                          p(mask), p(lse), p(dK), p(dQ), p(dV), p(s1), p(s2),
                                          p(s3)) == 13
         else:
