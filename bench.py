@@ -266,9 +266,12 @@ def rope_(x, base=10000.0):
     x.copy_(out.to(x.dtype))
 
 
-def causal_mask_tile(S, kind, device):
-    """(Sq, Sk) additive bf16 mask tile: 'diag' = -inf where k > q, 'zero', 'ninf'."""
+def causal_mask_tile(S, kind, device, dtype=None):
+    """(Sq, Sk) additive mask tile (bf16 unless `dtype` says otherwise): 'diag' = -inf
+    where k > q, 'zero', 'ninf'."""
     import torch
+    if dtype is not None and dtype != torch.bfloat16:
+        return causal_mask_tile(S, kind, device).to(dtype)
     if kind == "zero":
         return torch.zeros((S, S), dtype=torch.bfloat16, device=device)
     if kind == "ninf":
@@ -283,32 +286,33 @@ class FlashWorkload:
     """Single-sequence-tile fused attention forward+backward through the tile-level
     C entry points (the task the reference's tile layer submits)."""
 
-    def __init__(self, cfg, device, seed, rope=True):
+    def __init__(self, cfg, device, seed, rope=True, dtype=None):
         import torch
         from nntile_b200 import ops
         self.ops, self.torch, self.cfg = ops, torch, cfg
+        dt = dtype or torch.bfloat16
         H, G, B, S, D = cfg["kv_heads"], cfg["group"], cfg["batch"], cfg["seq"], cfg["head"]
         g = torch.Generator(device=device).manual_seed(seed)
         shp = (H, G, B, S, D)
-        self.q = torch.randn(shp, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        self.q = torch.randn(shp, generator=g, device=device, dtype=torch.float32).to(dt)
         kv = torch.randn((2, H, 1, B, S, D), generator=g, device=device, dtype=torch.float32)
         # K, V ~ N(0,1) per KV head, replicated over the group as the reference does
-        self.k = kv[0].expand(H, G, B, S, D).contiguous().to(torch.bfloat16)
-        self.v = kv[1].expand(H, G, B, S, D).contiguous().to(torch.bfloat16)
+        self.k = kv[0].expand(H, G, B, S, D).contiguous().to(dt)
+        self.v = kv[1].expand(H, G, B, S, D).contiguous().to(dt)
         del kv
         if rope:
             rope_(self.q)
             rope_(self.k)
-        self.dy = torch.randn(shp, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
-        self.mask = causal_mask_tile(S, "diag", device)
+        self.dy = torch.randn(shp, generator=g, device=device, dtype=torch.float32).to(dt)
+        self.mask = causal_mask_tile(S, "diag", device, dt)
         self.nb = H*G*B
         self.S, self.D = S, D
-        self.y = torch.zeros(shp, dtype=torch.bfloat16, device=device)
+        self.y = torch.zeros(shp, dtype=dt, device=device)
         self.lse = torch.empty((H, G, B, S), dtype=torch.float32, device=device)
-        self.dq, self.dk, self.dv = (torch.zeros(shp, dtype=torch.bfloat16, device=device)
+        self.dq, self.dk, self.dv = (torch.zeros(shp, dtype=dt, device=device)
                                      for _ in range(3))
         self.s_lse = torch.empty_like(self.lse)
-        self.s1, self.s2, self.s3 = (torch.empty(shp, dtype=torch.bfloat16, device=device)
+        self.s1, self.s2, self.s3 = (torch.empty(shp, dtype=dt, device=device)
                                      for _ in range(3))
         self.flops_fwd, self.flops_bwd = causal_flops(cfg)
 
@@ -742,6 +746,13 @@ def run_extras(torch, ops, lib, dev, peaks, args):
     out["c4_long_context"] = run_c4(torch, ops, lib, dev, steps)
     # ---- config 3 through the grouped-query entry points (K, V not replicated)
     out["c3_native_gqa"] = run_c3_gqa(torch, ops, dev, steps)
+    # ---- config 3 in IEEE half: the fp16 build of the same kernels
+    wl = FlashWorkload(C3, dev, seed=2, dtype=torch.float16)
+    ms, _, _ = time_steps(torch, wl.step, steps, 3)
+    ms /= steps
+    out["c3_fp16"] = {"tflops": (wl.flops_fwd + wl.flops_bwd)/(ms*1e-3)/1e12, "ms_per_step": ms,
+                      "note": "config 3 with fp16 storage through nntile_b200_flash_sdpa_{fwd,bwd}_fp16"}
+    del wl
     # ---- config 5: decode, HBM-bound
     out["c5_decode"] = run_decode(torch, ops, dev, peaks, C5, steps*4, 5)
     try:

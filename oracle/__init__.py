@@ -72,8 +72,9 @@ def ref_gpu():
             _ref_gpu = None
         if _ref_gpu is not None:
             vp, i64 = ctypes.c_void_p, ctypes.c_int64
-            _ref_gpu.refgpu_flash_sdpa_fwd_bf16.argtypes = [vp, i64, i64, i64] + [vp]*8
-            _ref_gpu.refgpu_flash_sdpa_bwd_bf16.argtypes = [vp, i64, i64, i64] + [vp]*13
+            for sfx in ("bf16", "fp16"):
+                getattr(_ref_gpu, f"refgpu_flash_sdpa_fwd_{sfx}").argtypes = [vp, i64, i64, i64] + [vp]*8
+                getattr(_ref_gpu, f"refgpu_flash_sdpa_bwd_{sfx}").argtypes = [vp, i64, i64, i64] + [vp]*13
     return _ref_gpu
 
 

@@ -27,7 +27,8 @@ namespace nk = nntile::kernel;
 using nntile::bf16_t;
 using nntile::fp32_t;
 typedef std::int64_t i64;
-typedef std::tuple<i64, i64, i64> Key;
+
+typedef std::tuple<int, i64, i64, i64> Key;       // (fp16?, seq, head, batch)
 
 struct BwdEntry
 {
@@ -50,52 +51,74 @@ static bool ensure_handle(void *stream)
 }
 
 // 0 = enqueued, 1 = no cuDNN handle, 2 = prepare_graph returned null
-extern "C" int refgpu_flash_sdpa_fwd_bf16(void *stream, i64 seq, i64 head, i64 batch,
+template<typename T>
+static int run_fwd(int fp16, void *stream, i64 seq, i64 head, i64 batch,
         const void *K, const void *Q, const void *mask, void *scratch_lse, const void *V,
         void *scratch_A, void *lse, void *A)
 {
     if(!ensure_handle(stream)) return 1;
-    const Key key(seq, head, batch);
+    const Key key(fp16, seq, head, batch);
     auto it = g_fwd.find(key);
     if(it == g_fwd.end())
     {
-        auto graph = nk::flash_sdpa_fwd_cudnn::prepare_graph<bf16_t>(g_handle, seq, head, batch);
+        auto graph = nk::flash_sdpa_fwd_cudnn::prepare_graph<T>(g_handle, seq, head, batch);
         if(!graph) return 2;
         it = g_fwd.emplace(key, graph).first;
     }
-    nk::flash_sdpa_fwd_cudnn::execute_graph<bf16_t>(g_handle, it->second, seq, head, batch,
-            static_cast<const bf16_t *>(K), static_cast<const bf16_t *>(Q),
-            static_cast<const bf16_t *>(mask), static_cast<fp32_t *>(scratch_lse),
-            static_cast<const bf16_t *>(V), static_cast<bf16_t *>(scratch_A),
-            static_cast<fp32_t *>(lse), static_cast<bf16_t *>(A));
+    nk::flash_sdpa_fwd_cudnn::execute_graph<T>(g_handle, it->second, seq, head, batch,
+            static_cast<const T *>(K), static_cast<const T *>(Q),
+            static_cast<const T *>(mask), static_cast<fp32_t *>(scratch_lse),
+            static_cast<const T *>(V), static_cast<T *>(scratch_A),
+            static_cast<fp32_t *>(lse), static_cast<T *>(A));
     return 0;
 }
 
-extern "C" int refgpu_flash_sdpa_bwd_bf16(void *stream, i64 seq, i64 head, i64 batch,
+template<typename T>
+static int run_bwd(int fp16, void *stream, i64 seq, i64 head, i64 batch,
         const void *K, const void *Q, const void *V, const void *A, const void *dA,
         const void *mask, const void *lse, void *scratch_dK, void *scratch_dQ,
         void *scratch_dV, void *dK, void *dQ, void *dV)
 {
     if(!ensure_handle(stream)) return 1;
-    const Key key(seq, head, batch);
+    const Key key(fp16, seq, head, batch);
     auto it = g_bwd.find(key);
     if(it == g_bwd.end())
     {
         BwdEntry e;
-        e.graph = nk::flash_sdpa_bwd_cudnn::prepare_graph<bf16_t>(g_handle, seq, head, batch);
+        e.graph = nk::flash_sdpa_bwd_cudnn::prepare_graph<T>(g_handle, seq, head, batch);
         if(!e.graph) return 2;
         ::int64_t ws = 0;
         if(!e.graph->get_workspace_size(ws).is_good()) return 3;
         if(ws > 0 && cudaMalloc(&e.workspace, (size_t)ws) != cudaSuccess) return 3;
         it = g_bwd.emplace(key, e).first;
     }
-    nk::flash_sdpa_bwd_cudnn::execute_graph<bf16_t>(g_handle, it->second.graph, seq, head,
-            batch, static_cast<const bf16_t *>(K), static_cast<const bf16_t *>(Q),
-            static_cast<const bf16_t *>(V), static_cast<const bf16_t *>(A),
-            static_cast<const bf16_t *>(dA), static_cast<const bf16_t *>(mask),
-            static_cast<const fp32_t *>(lse), static_cast<bf16_t *>(scratch_dK),
-            static_cast<bf16_t *>(scratch_dQ), static_cast<bf16_t *>(scratch_dV),
-            static_cast<bf16_t *>(dK), static_cast<bf16_t *>(dQ), static_cast<bf16_t *>(dV),
+    nk::flash_sdpa_bwd_cudnn::execute_graph<T>(g_handle, it->second.graph, seq, head,
+            batch, static_cast<const T *>(K), static_cast<const T *>(Q),
+            static_cast<const T *>(V), static_cast<const T *>(A),
+            static_cast<const T *>(dA), static_cast<const T *>(mask),
+            static_cast<const fp32_t *>(lse), static_cast<T *>(scratch_dK),
+            static_cast<T *>(scratch_dQ), static_cast<T *>(scratch_dV),
+            static_cast<T *>(dK), static_cast<T *>(dQ), static_cast<T *>(dV),
             it->second.workspace);
     return 0;
 }
+
+#define REFGPU(suffix, TYPE, FLAG) \
+extern "C" int refgpu_flash_sdpa_fwd_##suffix(void *stream, i64 seq, i64 head, i64 batch, \
+        const void *K, const void *Q, const void *mask, void *scratch_lse, const void *V, \
+        void *scratch_A, void *lse, void *A) \
+{ \
+    return run_fwd<TYPE>(FLAG, stream, seq, head, batch, K, Q, mask, scratch_lse, V, scratch_A, \
+            lse, A); \
+} \
+extern "C" int refgpu_flash_sdpa_bwd_##suffix(void *stream, i64 seq, i64 head, i64 batch, \
+        const void *K, const void *Q, const void *V, const void *A, const void *dA, \
+        const void *mask, const void *lse, void *scratch_dK, void *scratch_dQ, \
+        void *scratch_dV, void *dK, void *dQ, void *dV) \
+{ \
+    return run_bwd<TYPE>(FLAG, stream, seq, head, batch, K, Q, V, A, dA, mask, lse, scratch_dK, \
+            scratch_dQ, scratch_dV, dK, dQ, dV); \
+}
+
+REFGPU(bf16, bf16_t, 0)
+REFGPU(fp16, nntile::fp16_t, 1)

@@ -24,24 +24,29 @@ def rel(a, b):
     return float((a.float() - b.float()).norm()/b.float().norm())
 
 
-@pytest.mark.parametrize("seq,head,batch,kind", [
-    (256, 64, 6, "causal"),      # the reference's Python flash case (head 64, seq 256)
-    (512, 128, 4, "causal"),
-    (256, 128, 3, "band"),       # |q - k| <= 32, the reference tests' banded mask
-    (128, 64, 2, "none"),
+@pytest.mark.parametrize("seq,head,batch,kind,dtype", [
+    (256, 64, 6, "causal", torch.bfloat16),   # the reference's Python flash case (head 64, seq 256)
+    (512, 128, 4, "causal", torch.bfloat16),
+    (256, 128, 3, "band", torch.bfloat16),    # |q - k| <= 32, the reference tests' banded mask
+    (128, 64, 2, "none", torch.bfloat16),
+    (256, 128, 2, "causal", torch.float16),   # the fp16 instantiation of both sides
+    (256, 64, 3, "band", torch.float16),
 ])
-def test_reference_gpu_wrappers_agree_with_the_c_abi(seq, head, batch, kind):
+def test_reference_gpu_wrappers_agree_with_the_c_abi(seq, head, batch, kind, dtype):
     ref = O.ref_gpu()
     if ref is None:
         pytest.skip("oracle/_ref_gpu not built (needs the reference checkout at build time)")
     g = torch.Generator(device="cuda").manual_seed(seq + head)
-    mk = lambda: torch.randn((batch, seq, head), generator=g, device="cuda").to(torch.bfloat16)
+    mk = lambda: torch.randn((batch, seq, head), generator=g, device="cuda").to(dtype)
+    sfx = "fp16" if dtype == torch.float16 else "bf16"
+    ref_fwd = getattr(ref, f"refgpu_flash_sdpa_fwd_{sfx}")
+    ref_bwd = getattr(ref, f"refgpu_flash_sdpa_bwd_{sfx}")
     Q, K, V, dA = mk(), mk(), mk(), mk()
     qi = torch.arange(seq, device="cuda")[:, None]
     ki = torch.arange(seq, device="cuda")[None, :]
     keep = {"causal": ki <= qi, "band": (qi - ki).abs() <= 32,
             "none": torch.ones((seq, seq), dtype=torch.bool, device="cuda")}[kind]
-    mask = torch.where(keep, 0.0, -math.inf).to(torch.bfloat16)       # [q][k] row major
+    mask = torch.where(keep, 0.0, -math.inf).to(dtype)                # [q][k] row major
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     # the reference's execute_graph refuses the null stream for its add passes
     side = torch.cuda.Stream()
@@ -54,13 +59,13 @@ def test_reference_gpu_wrappers_agree_with_the_c_abi(seq, head, batch, kind):
         s_l, s1, s2, s3 = torch.empty_like(lse), torch.empty_like(Q), torch.empty_like(Q), \
             torch.empty_like(Q)
         dK, dQ, dV = (torch.full_like(Q, 0.25) for _ in range(3))
-        K2 = (K.float()*0.5).to(torch.bfloat16)
+        K2 = (K.float()*0.5).to(dtype)
         with torch.cuda.stream(side):
             side.wait_stream(torch.cuda.default_stream())
             sp = ctypes.c_void_p(side.cuda_stream)
             for kk in (K, K2):
                 if who == "ref":
-                    st = ref.refgpu_flash_sdpa_fwd_bf16(sp, seq, head, batch, p(kk), p(Q), p(mask),
+                    st = ref_fwd(sp, seq, head, batch, p(kk), p(Q), p(mask),
                                                         p(s_l), p(V), p(s1), p(lse), p(A))
                     if st == 2:
                         pytest.skip("cuDNN did not build the reference's forward graph here")
@@ -72,7 +77,7 @@ def test_reference_gpu_wrappers_agree_with_the_c_abi(seq, head, batch, kind):
             # backward of the FIRST tile against the merged A and lse, as the
             # reference's tensor loop calls it
             if who == "ref":
-                st = ref.refgpu_flash_sdpa_bwd_bf16(sp, seq, head, batch, p(K), p(Q), p(V), p(Afin),
+                st = ref_bwd(sp, seq, head, batch, p(K), p(Q), p(V), p(Afin),
                                                     p(dA), p(mask), p(lfin), p(s1), p(s2), p(s3),
                                                     p(dK), p(dQ), p(dV))
                 if st == 2:
