@@ -404,17 +404,34 @@ static DecodePlan decode_plan(Index head, Index length, Index batch, Index group
 {
     DecodePlan p;
     p.fast = (head == 64 || head == 128) && group >= 1 && group <= 8;
-    // Chunk length: long chunks amortise the per-CTA prologue and merge (measured on
-    // config 5: 512 keys per CTA 5.2 TB/s, 1024 5.6, 2048 6.0, 4096 5.5), as long as
-    // about four to five waves of CTAs (148 SMs x 3 resident) remain for balance.
+    // Chunks per cache unit.  Two things cost: a CTA's fixed part (prologue, the
+    // exposed latency of its first loads, the partial result it writes: worth about
+    // 600 key rows of streaming) and a last wave of CTAs that leaves SMs idle (148 SMs
+    // x 3 resident CTAs).  Every candidate is scored as waves x (rows per chunk + 600)
+    // and the cheapest wins.  Measured on config 5's cache length (8192) this picks
+    // 4 chunks at 512 units (0.36 ms, 0.92 of the copy bandwidth), 3 at 256 and 128
+    // units, 6 at 64 units (58 us against 105 us with the former "about 2048 CTAs"
+    // rule) - the per-GPU shares of config 5 on 1, 2, 4 and 8 GPUs.
     // The fast kernel shares a chunk among the query heads of a group, the generic
     // one runs one CTA row per query head.
     const Index units = p.fast ? batch*kv_heads : batch*group*kv_heads;
-    Index nsplit = (2048 + units - 1)/units;
-    const Index max_split = (length + 255)/256;          // at least 256 keys per chunk
-    if(nsplit > max_split) nsplit = max_split;
-    if(nsplit > 64) nsplit = 64;
-    if(nsplit < 1) nsplit = 1;
+    const Index resident = 148*3;
+    Index max_split = (length + 255)/256;                // at least 256 keys per chunk
+    if(max_split > 64) max_split = 64;
+    if(max_split < 1) max_split = 1;
+    Index nsplit = 1, best = -1;
+    for(Index n = 1; n <= max_split; ++n)
+    {
+        Index r = (length + n - 1)/n;
+        r = (r + 63)/64*64;
+        const Index waves = (units*n + resident - 1)/resident;
+        const Index cost = waves*(r + 600);
+        if(best < 0 || cost < best)
+        {
+            best = cost;
+            nsplit = n;
+        }
+    }
     Index rows = (length + nsplit - 1)/nsplit;
     rows = (rows + 63)/64*64;                            // whole steps of the 4 warps
     p.rows_per_cta = (int)rows;
