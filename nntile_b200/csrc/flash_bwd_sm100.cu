@@ -955,7 +955,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
 } // namespace bwd
 
-#ifdef NB200_PROF
+#if defined(NB200_PROF) && !defined(NB200_FP16)
 extern "C" void nntile_b200_debug_prof_bwd(unsigned long long *out32, int reset)
 {
     cudaDeviceSynchronize();

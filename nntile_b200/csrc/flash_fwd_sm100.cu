@@ -811,7 +811,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
 } // namespace fwd
 
-#ifdef NB200_PROF
+#if defined(NB200_PROF) && !defined(NB200_FP16)
 extern "C" void nntile_b200_debug_prof(unsigned long long *out16, int reset)
 {
     cudaDeviceSynchronize();
