@@ -64,7 +64,8 @@ __device__ unsigned long long g_prof[32];
 #define PROF_DECL unsigned long long prof_loc[32]; for(int i_ = 0; i_ < 32; ++i_) prof_loc[i_] = 0
 #define PROF_ADD(slot, a, b) prof_loc[slot] += (unsigned long long)((b) - (a))
 #define PROF_INC(slot) prof_loc[slot] += 1ull
-#define PROF_FLUSH for(int i_ = 0; i_ < 32; ++i_) if(prof_loc[i_]) atomicAdd(&g_prof[i_], prof_loc[i_])
+#define PROF_FLUSH if((threadIdx.x >> 5) != 1 || (threadIdx.x & 31) == 0) \
+    for(int i_ = 0; i_ < 32; ++i_) if(prof_loc[i_]) atomicAdd(&g_prof[i_], prof_loc[i_])
 #else
 #define PROF_T(var)
 #define PROF_DECL
@@ -429,47 +430,65 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
     else if(warp == 1)
     {
         // ================================ MMA issuer ===========================
-        if(lane == 0 && nact > 0)
+        // (all 32 lanes walk the loop with warp-wide waits; one elected lane issues, so
+        // that the operand descriptors are formed in converged code)
+        if(nact > 0)
         {
             // Issue order.  The loop-carried chain is
             //   dS^T(n) -> dK(n), dQ(n) -> drain -> dP^T(n+1) -> dS^T(n+1);
             // dV(n+1) is slotted into the drain window and S^T(n+2) behind dP^T(n+1),
             // where the softmax warps are busy with dS^T(n+1), so the tensor pipe
             // has work whenever the chain leaves it idle.
-            bool ok = mbar_wait(&sm.kv_full, 0, abort_flag);
-            ok = ok && mbar_wait(&sm.q_full[0], 0, abort_flag);
+            bool ok = mbar_wait_warp(&sm.kv_full, 0, abort_flag);
+            ok = ok && mbar_wait_warp(&sm.q_full[0], 0, abort_flag);
             if(ok)
             {
                 tc_fence_after_sync();
-                issue_kmajor<D>(st_tm, sm.k, sm.q[0]);               // S^T(0)
-                tc_commit(&sm.s_full);
-            }
-            ok = ok && mbar_wait(&sm.g_full[0], 0, abort_flag);
-            if(ok)
-            {
-                tc_fence_after_sync();
-                issue_kmajor<D>(dpt_tm, sm.v, sm.g[0]);              // dP^T(0)
-                tc_commit(&sm.dp_full);
-            }
-            ok = ok && mbar_wait(&sm.p_full, 0, abort_flag);
-            if(ok)
-            {
-                tc_fence_after_sync();
-                issue_ts<D>(dv_tm, st_tm, sm.g[0], false);           // dV = P^T(0) dO
-                tc_commit(&sm.g_empty[0]);
-                if(nact == 1)
+                if(elect_one())
                 {
-                    tc_commit(&sm.dv_full);      // dV is complete one step before dK
+                    issue_kmajor<D>(st_tm, sm.k, sm.q[0]);           // S^T(0)
+                    tc_commit(&sm.s_full);
                 }
+                __syncwarp();
+            }
+            ok = ok && mbar_wait_warp(&sm.g_full[0], 0, abort_flag);
+            if(ok)
+            {
+                tc_fence_after_sync();
+                if(elect_one())
+                {
+                    issue_kmajor<D>(dpt_tm, sm.v, sm.g[0]);          // dP^T(0)
+                    tc_commit(&sm.dp_full);
+                }
+                __syncwarp();
+            }
+            ok = ok && mbar_wait_warp(&sm.p_full, 0, abort_flag);
+            if(ok)
+            {
+                tc_fence_after_sync();
+                if(elect_one())
+                {
+                    issue_ts<D>(dv_tm, st_tm, sm.g[0], false);       // dV = P^T(0) dO
+                    tc_commit(&sm.g_empty[0]);
+                    if(nact == 1)
+                    {
+                        tc_commit(&sm.dv_full);  // dV is complete one step before dK
+                    }
+                }
+                __syncwarp();
             }
             if(ok && nact > 1)
             {
-                ok = mbar_wait(&sm.q_full[1], 0, abort_flag);
+                ok = mbar_wait_warp(&sm.q_full[1], 0, abort_flag);
                 if(ok)
                 {
                     tc_fence_after_sync();
-                    issue_kmajor<D>(st_tm, sm.k, sm.q[1]);           // S^T(1)
-                    tc_commit(&sm.s_full);
+                    if(elect_one())
+                    {
+                        issue_kmajor<D>(st_tm, sm.k, sm.q[1]);       // S^T(1)
+                        tc_commit(&sm.s_full);
+                    }
+                    __syncwarp();
                 }
             }
             bool s_pending = false;
@@ -477,34 +496,46 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
             {
                 const int st = n & 1, s2 = (n + 1) & 1;
                 PROF_T(m0);
-                ok = mbar_wait(&sm.ds_full, (uint32_t)n & 1u, abort_flag);
+                ok = mbar_wait_warp(&sm.ds_full, (uint32_t)n & 1u, abort_flag);
                 if(!ok) break;
                 tc_fence_after_sync();
                 PROF_T(m1);
-                issue_ts<D>(dk_tm, dpt_tm, sm.q[st], n > 0);         // dK += dS^T Q
-                tc_commit(&sm.q_empty[st]);
+                if(elect_one())
+                {
+                    issue_ts<D>(dk_tm, dpt_tm, sm.q[st], n > 0);     // dK += dS^T Q
+                    tc_commit(&sm.q_empty[st]);
+                }
+                __syncwarp();
                 if(!ALIAS && n > 0)
                 {
-                    ok = mbar_wait(&sm.dq_empty, (uint32_t)(n - 1) & 1u, abort_flag);
+                    ok = mbar_wait_warp(&sm.dq_empty, (uint32_t)(n - 1) & 1u, abort_flag);
                     if(!ok) break;
                     tc_fence_after_sync();
                 }
-                if(DQ_TRANSPOSED)
+                if(elect_one())
                 {
-                    issue_dq<D>(dq_tm, sm.k, sm.ds);                 // dQ_i^T = K^T dS^T
+                    if(DQ_TRANSPOSED)
+                    {
+                        issue_dq<D>(dq_tm, sm.k, sm.ds);             // dQ_i^T = K^T dS^T
+                    }
+                    else
+                    {
+                        issue_dq<D>(dq_tm, sm.ds, sm.k);             // dQ_i = dS K
+                    }
+                    tc_commit(&sm.dq_full);
                 }
-                else
-                {
-                    issue_dq<D>(dq_tm, sm.ds, sm.k);                 // dQ_i = dS K
-                }
-                tc_commit(&sm.dq_full);
+                __syncwarp();
                 if(s_pending)
                 {
-                    ok = mbar_wait(&sm.q_full[s2], (uint32_t)((n + 1) >> 1) & 1u, abort_flag);
+                    ok = mbar_wait_warp(&sm.q_full[s2], (uint32_t)((n + 1) >> 1) & 1u, abort_flag);
                     if(!ok) break;
                     tc_fence_after_sync();
-                    issue_kmajor<D>(st_tm, sm.k, sm.q[s2]);          // the deferred S^T(n+1)
-                    tc_commit(&sm.s_full);
+                    if(elect_one())
+                    {
+                        issue_kmajor<D>(st_tm, sm.k, sm.q[s2]);      // the deferred S^T(n+1)
+                        tc_commit(&sm.s_full);
+                    }
+                    __syncwarp();
                     s_pending = false;
                 }
                 PROF_T(m2);
@@ -519,55 +550,78 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #endif
                 if(n + 1 >= nact)
                 {
-                    tc_commit(&sm.acc_full);
+                    if(elect_one())
+                    {
+                        tc_commit(&sm.acc_full);
+                    }
+                    __syncwarp();
                     break;
                 }
                 const uint32_t ph1 = (uint32_t)((n + 1) >> 1) & 1u;
-                ok = mbar_wait(&sm.g_full[s2], ph1, abort_flag);
+                ok = mbar_wait_warp(&sm.g_full[s2], ph1, abort_flag);
                 if(!ok) break;
                 PROF_T(m3);
                 // dV(n+1) goes first only if P^T(n+1) is already there; otherwise the
                 // chain (dP^T) must not wait for it
                 bool dv_issued = false;
-                if(mbar_try_wait(&sm.p_full, (uint32_t)(n + 1) & 1u))
+                if(__all_sync(0xffffffffu, mbar_try_wait(&sm.p_full, (uint32_t)(n + 1) & 1u)))
                 {
                     tc_fence_after_sync();
-                    issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);       // dV += P^T(n+1) dO
+                    if(elect_one())
+                    {
+                        issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);   // dV += P^T(n+1) dO
+                    }
+                    __syncwarp();
                     dv_issued = true;
                 }
                 PROF_T(m4);
                 PROF_T(m5);
                 if(ALIAS)
                 {
-                    ok = mbar_wait(&sm.dq_empty, (uint32_t)n & 1u, abort_flag);
+                    ok = mbar_wait_warp(&sm.dq_empty, (uint32_t)n & 1u, abort_flag);
                     if(!ok) break;
                     tc_fence_after_sync();
                 }
                 PROF_T(m6);
-                issue_kmajor<D>(dpt_tm, sm.v, sm.g[s2]);             // dP^T(n+1)
-                tc_commit(&sm.dp_full);
+                if(elect_one())
+                {
+                    issue_kmajor<D>(dpt_tm, sm.v, sm.g[s2]);         // dP^T(n+1)
+                    tc_commit(&sm.dp_full);
+                }
+                __syncwarp();
                 if(!dv_issued)
                 {
-                    ok = mbar_wait(&sm.p_full, (uint32_t)(n + 1) & 1u, abort_flag);
+                    ok = mbar_wait_warp(&sm.p_full, (uint32_t)(n + 1) & 1u, abort_flag);
                     if(!ok) break;
                     tc_fence_after_sync();
-                    issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);       // dV += P^T(n+1) dO
                 }
-                tc_commit(&sm.g_empty[s2]);
-                if(n + 2 == nact)
+                if(elect_one())
                 {
-                    tc_commit(&sm.dv_full);
+                    if(!dv_issued)
+                    {
+                        issue_ts<D>(dv_tm, st_tm, sm.g[s2], true);   // dV += P^T(n+1) dO
+                    }
+                    tc_commit(&sm.g_empty[s2]);
+                    if(n + 2 == nact)
+                    {
+                        tc_commit(&sm.dv_full);
+                    }
                 }
+                __syncwarp();
                 PROF_T(m7);
                 if(n + 2 < nact)
                 {
                     // Q(n+2) reuses the stage dK(n) has just released; if its copy has
                     // not landed yet, S^T(n+2) is issued after the next dK, dQ instead
-                    if(mbar_try_wait(&sm.q_full[st], (uint32_t)((n + 2) >> 1) & 1u))
+                    if(__all_sync(0xffffffffu, mbar_try_wait(&sm.q_full[st], (uint32_t)((n + 2) >> 1) & 1u)))
                     {
                         tc_fence_after_sync();
-                        issue_kmajor<D>(st_tm, sm.k, sm.q[st]);      // S^T(n+2)
-                        tc_commit(&sm.s_full);
+                        if(elect_one())
+                        {
+                            issue_kmajor<D>(st_tm, sm.k, sm.q[st]);  // S^T(n+2)
+                            tc_commit(&sm.s_full);
+                        }
+                        __syncwarp();
                     }
                     else
                     {
@@ -587,7 +641,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 }
 #endif
             }
-            if(!ok)
+            if(!ok && lane == 0)
             {
                 atomicCAS(status, 0u, STATUS_BWD_MMA);
             }

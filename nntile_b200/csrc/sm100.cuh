@@ -112,6 +112,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
     }
 }
 
+// The same wait for a converged warp: every lane polls, and all lanes get the same
+// answer (a limit that ran out in one lane ends the wait for the warp).
+template<uint64_t LIMIT_NS = WAIT_LIMIT_NS>
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity,
+        volatile uint32_t *abort_flag)
+{
+    return __all_sync(0xffffffffu, mbar_wait<LIMIT_NS>(bar, parity, abort_flag));
+}
+
 // ------------------------------------------------------------------------ TMA
 // 2-D tiled load global -> this CTA's shared memory, completion on an mbarrier.
 // x is the innermost (contiguous) coordinate: x * element size must be a
