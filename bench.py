@@ -732,8 +732,17 @@ def run_hbm_kernels(torch, ops, dev, peaks, steps):
         out[f"sumprod_slice_{tag}"] = timed(
             lambda: ops.sumprod_slice(1, Sq*nbatch, Sk, 1.0, logits, other, 0.0, sl), 2*nb)
         del logits, other, mse, sl
-    out["note"] = ("mask_scalar writes only the masked half (causal); bytes are algorithmic, "
-                   "peak = measured copy bandwidth")
+    # a write-only kernel cannot reach the copy figure (reads + writes): a plain fill of
+    # 1 GiB (torch's zero_) is the yardstick for mask_scalar, which only writes
+    big = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    fill = timed(lambda: big.zero_(), 1 << 30)
+    del big
+    out["fill_1gib_torch_zero"] = fill
+    for tag in ("bf16", "fp32"):
+        out[f"mask_scalar_{tag}"]["frac_of_fill"] = out[f"mask_scalar_{tag}"]["gbs"]/fill["gbs"]
+    out["note"] = ("mask_scalar writes only the masked half (causal) and reads nothing but the mask: "
+                   "its yardstick is the write-only rate (fill_1gib_torch_zero), not the copy bandwidth; "
+                   "bytes are algorithmic, peak = measured copy bandwidth")
     return out
 
 

@@ -15,7 +15,9 @@
 // grouped-query entry points of the fused pair there is no K/V replication pass
 // (add_slice_inplace) left either.
 //
-// One CTA handles `tp` consecutive (seq, batch) positions at a time: their
+// Two forms.  With lead a multiple of 8 a thread transposes an 8 x 8 block in
+// registers (transpose_in_reg_kernel below).  Otherwise (lead even, e.g. 12 heads)
+// one CTA handles `tp` consecutive (seq, batch) positions at a time: their
 // lead*head*tp source elements are one contiguous run, and for every value of
 // `lead` the tp*head destination elements are one contiguous run too.  The run is
 // staged in shared memory transposed, as tile[lead index][position*head + d], so
@@ -195,6 +197,132 @@ transpose_out_kernel(int lead, int head, Index npos, int tp, int swz, const bf16
     }
 }
 
+// ---- lead a multiple of 8: no staging at all.  The tensor is a [rows = position*head]
+// x [lead] matrix to transpose; a thread takes an 8 x 8 block of it as eight 16-byte
+// loads (eight consecutive rows, which lie in one position because head is a
+// multiple of 8), transposes it in registers with byte permutes and writes eight
+// 16-byte pieces, one per lead index.  Consecutive threads take consecutive column
+// blocks of the same rows, then the next rows: a warp's loads cover whole 32-byte
+// sectors and its stores are runs of at least 128 bytes.
+__device__ __forceinline__ uint4 pro_column(const uint4 (&in)[8], int e)
+{
+    // 16-bit element e of each of the eight pieces, in order
+    const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+    uint32_t w[4];
+#pragma unroll
+    for(int k = 0; k < 4; ++k)
+    {
+        const uint32_t a = (e >> 1) == 0 ? in[2*k].x : (e >> 1) == 1 ? in[2*k].y
+                : (e >> 1) == 2 ? in[2*k].z : in[2*k].w;
+        const uint32_t b = (e >> 1) == 0 ? in[2*k + 1].x : (e >> 1) == 1 ? in[2*k + 1].y
+                : (e >> 1) == 2 ? in[2*k + 1].z : in[2*k + 1].w;
+        w[k] = __byte_perm(a, b, sel);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template<int MODE>
+__global__ void __launch_bounds__(PRO_THREADS)
+transpose_in_reg_kernel(int lead, int head, Index nrows, const bf16 *__restrict__ aux0,
+        const bf16 *__restrict__ aux1, const bf16 *__restrict__ src, bf16 *__restrict__ dst)
+{
+    const int pb = lead >> 3;
+    const Index items = (nrows >> 3)*pb;
+    for(Index v = (Index)blockIdx.x*PRO_THREADS + threadIdx.x; v < items;
+            v += (Index)gridDim.x*PRO_THREADS)
+    {
+        const Index rg = v/pb;
+        const int p = (int)(v - rg*pb);
+        const Index r0 = rg << 3;
+        const uint4 *g = reinterpret_cast<const uint4 *>(src + r0*lead + 8*p);
+        uint4 in[8];
+#pragma unroll
+        for(int r = 0; r < 8; ++r)
+        {
+            in[r] = g[(Index)r*pb];
+        }
+        uint32_t sw[2] = {0u, 0u}, cw[2] = {0u, 0u};
+        if(MODE == PRO_ROPE)
+        {
+            // (position, d/2) index of the first of the four pairs of these rows
+            const uint2 sv = *reinterpret_cast<const uint2 *>(aux0 + (r0 >> 1));
+            const uint2 cv = *reinterpret_cast<const uint2 *>(aux1 + (r0 >> 1));
+            sw[0] = sv.x; sw[1] = sv.y; cw[0] = cv.x; cw[1] = cv.y;
+        }
+#pragma unroll
+        for(int e = 0; e < 8; ++e)
+        {
+            const uint4 col = pro_column(in, e);
+            uint32_t w[4] = {col.x, col.y, col.z, col.w};
+            const int n = 8*p + e;
+            if(MODE == PRO_ROPE)
+            {
+#pragma unroll
+                for(int q = 0; q < 4; ++q)
+                {
+                    const uint32_t sb = sw[q >> 1], cb = cw[q >> 1];
+                    const float sn = __uint_as_float((q & 1) ? (sb & 0xFFFF0000u) : (sb << 16));
+                    const float co = __uint_as_float((q & 1) ? (cb & 0xFFFF0000u) : (cb << 16));
+                    const float a = __uint_as_float(w[q] << 16);
+                    const float b = __uint_as_float(w[q] & 0xFFFF0000u);
+                    w[q] = pro_bf16x2(__fsub_rn(__fmul_rn(co, a), __fmul_rn(sn, b)),
+                            __fadd_rn(__fmul_rn(sn, a), __fmul_rn(co, b)));
+                }
+            }
+            else if(MODE == PRO_BIAS)
+            {
+                // bias[d, n], d fastest
+                const int d = (int)(r0 % head);
+                const uint4 bv = *reinterpret_cast<const uint4 *>(aux0 + (Index)n*head + d);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for(int q = 0; q < 4; ++q)
+                {
+                    w[q] = pro_bf16x2(
+                            __fadd_rn(__uint_as_float(w[q] << 16), __uint_as_float(bw[q] << 16)),
+                            __fadd_rn(__uint_as_float(w[q] & 0xFFFF0000u),
+                                    __uint_as_float(bw[q] & 0xFFFF0000u)));
+                }
+            }
+            *reinterpret_cast<uint4 *>(dst + (Index)n*nrows + r0) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(PRO_THREADS)
+transpose_out_reg_kernel(int lead, Index nrows, const bf16 *__restrict__ src, bf16 *__restrict__ dst)
+{
+    const int pb = lead >> 3;
+    const Index items = (nrows >> 3)*pb;
+    for(Index v = (Index)blockIdx.x*PRO_THREADS + threadIdx.x; v < items;
+            v += (Index)gridDim.x*PRO_THREADS)
+    {
+        const Index rg = v/pb;
+        const int p = (int)(v - rg*pb);
+        const Index r0 = rg << 3;
+        uint4 in[8];
+#pragma unroll
+        for(int e = 0; e < 8; ++e)
+        {
+            in[e] = *reinterpret_cast<const uint4 *>(src + (Index)(8*p + e)*nrows + r0);
+        }
+        uint4 *g = reinterpret_cast<uint4 *>(dst + r0*lead + 8*p);
+#pragma unroll
+        for(int r = 0; r < 8; ++r)
+        {
+            g[(Index)r*pb] = pro_column(in, r);
+        }
+    }
+}
+
+static unsigned pro_reg_grid(int lead, Index nrows)
+{
+    const Index items = (nrows >> 3)*(lead >> 3);
+    const Index blocks = (items + PRO_THREADS - 1)/PRO_THREADS;
+    const Index cap = 148*16;
+    return (unsigned)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
 struct ProPlan
 {
     int tp, swz;
@@ -256,6 +384,23 @@ extern "C" int nntile_b200_transpose_rope_bf16(nntile_b200_stream_t stream, int6
     {
         return NNTILE_B200_E_ALIGN;
     }
+    if(lead % 8 == 0)
+    {
+        const Index nrows = npos*head;
+        const unsigned grid = pro_reg_grid((int)lead, nrows);
+        if(sin)
+        {
+            transpose_in_reg_kernel<PRO_ROPE><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead,
+                    (int)head, nrows, (const bf16 *)sin, (const bf16 *)cos, (const bf16 *)src,
+                    (bf16 *)dst);
+        }
+        else
+        {
+            transpose_in_reg_kernel<PRO_PLAIN><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead,
+                    (int)head, nrows, nullptr, nullptr, (const bf16 *)src, (bf16 *)dst);
+        }
+        return launch_status();
+    }
     const ProPlan p = pro_plan((int)lead, (int)head, npos);
     if(p.smem > 200*1024) return NNTILE_B200_E_SHAPE;
     if(sin)
@@ -287,6 +432,14 @@ extern "C" int nntile_b200_transpose_bias_bf16(nntile_b200_stream_t stream, int6
     {
         return NNTILE_B200_E_ALIGN;
     }
+    if(lead % 8 == 0)
+    {
+        const Index nrows = npos*head;
+        transpose_in_reg_kernel<PRO_BIAS><<<pro_reg_grid((int)lead, nrows), PRO_THREADS, 0,
+                as_stream(stream)>>>((int)lead, (int)head, nrows, (const bf16 *)bias, nullptr,
+                (const bf16 *)src, (bf16 *)dst);
+        return launch_status();
+    }
     const ProPlan p = pro_plan((int)lead, (int)head, npos);
     if(p.smem > 200*1024) return NNTILE_B200_E_SHAPE;
     if(!pro_optin(transpose_in_kernel<PRO_BIAS>, p.smem)) return NNTILE_B200_E_LAUNCH;
@@ -304,6 +457,13 @@ extern "C" int nntile_b200_transpose_heads_back_bf16(nntile_b200_stream_t stream
     if(lead == 0 || head == 0 || npos == 0) return NNTILE_B200_OK;
     if(!src || !dst) return NNTILE_B200_E_BADARG;
     if(!aligned16(dst) || !aligned16(src)) return NNTILE_B200_E_ALIGN;
+    if(lead % 8 == 0)
+    {
+        const Index nrows = npos*head;
+        transpose_out_reg_kernel<<<pro_reg_grid((int)lead, nrows), PRO_THREADS, 0, as_stream(stream)>>>(
+                (int)lead, nrows, (const bf16 *)src, (bf16 *)dst);
+        return launch_status();
+    }
     const ProPlan p = pro_plan((int)lead, (int)head, npos);
     if(p.smem > 200*1024) return NNTILE_B200_E_SHAPE;
     if(!pro_optin(transpose_out_kernel, p.smem)) return NNTILE_B200_E_LAUNCH;

@@ -264,36 +264,60 @@ __global__ void maxsumexp_m1_kernel(Index n, Index k, const T *src, T *dst)
     }
 }
 
-// m == 1, vector form: `lpf` lanes share a fibre and walk it in 16-byte pieces.  Per
-// piece: the maximum of its finite values, one rescale of the running sum when the
-// maximum grows, then one exponential per value (exp(-inf) = 0 drops masked ones).
+// m == 1, vector form: `lpf` lanes share a fibre and walk it in 16-byte pieces, four
+// pieces (four independent loads) per pass.  Per pass: the maximum of the finite
+// values, one rescale of the running sum when the maximum grows, then one
+// exponential per value of every piece that has a finite one (exp(-inf) = 0 drops
+// masked values; a fully masked piece costs no exponentials).
 template<typename T>
 __global__ void __launch_bounds__(256)
 maxsumexp_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ src, T *dst)
 {
     constexpr int N = Vec<T>::N;
+    constexpr int U = 4;
     const int sub = threadIdx.x & (lpf - 1);
     const Index groups = ((Index)gridDim.x*blockDim.x)/lpf;
+    const Index step = (Index)lpf*N;
     for(Index j = ((Index)blockIdx.x*blockDim.x + threadIdx.x)/lpf; j < n; j += groups)
     {
         const T *fib = src + j*k;
         MaxSum acc = {-CUDART_INF_F, 0.0f};
         bool poisoned = false;
-        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        for(Index l0 = (Index)sub*N; l0 < k; l0 += step*U)
         {
-            float x[N];
-            vload(fib + l, x);
-            if(l == 0)
+            float x[U][N];
+            float ptop[U];
+#pragma unroll
+            for(int u = 0; u < U; ++u)
+            {
+                const Index l = l0 + (Index)u*step;
+                if(l < k)
+                {
+                    vload(fib + l, x[u]);
+                }
+                else
+                {
+#pragma unroll
+                    for(int e = 0; e < N; ++e) x[u][e] = -CUDART_INF_F;
+                }
+            }
+            if(l0 == 0)
             {
                 // a leading +inf makes the reference give up on the fibre
-                poisoned = isinf(x[0]) && x[0] > 0.0f;
+                poisoned = isinf(x[0][0]) && x[0][0] > 0.0f;
             }
             float top = -CUDART_INF_F;
 #pragma unroll
-            for(int e = 0; e < N; ++e)
+            for(int u = 0; u < U; ++u)
             {
-                x[e] = isinf(x[e]) ? -CUDART_INF_F : x[e];     // +inf is skipped like -inf
-                top = fmaxf(top, x[e]);
+                ptop[u] = -CUDART_INF_F;
+#pragma unroll
+                for(int e = 0; e < N; ++e)
+                {
+                    x[u][e] = isinf(x[u][e]) ? -CUDART_INF_F : x[u][e];     // +inf is skipped like -inf
+                    ptop[u] = fmaxf(ptop[u], x[u][e]);
+                }
+                top = fmaxf(top, ptop[u]);
             }
             if(top == -CUDART_INF_F)
             {
@@ -304,13 +328,21 @@ maxsumexp_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ src, T 
                 acc.sum *= exp_for(fib, acc.top - top);        // exp(-inf) = 0: empty pair
                 acc.top = top;
             }
-            float part = 0.0f;
 #pragma unroll
-            for(int e = 0; e < N; ++e)
+            for(int u = 0; u < U; ++u)
             {
-                part += exp_for(fib, x[e] - acc.top);
+                if(ptop[u] == -CUDART_INF_F)
+                {
+                    continue;
+                }
+                float part = 0.0f;
+#pragma unroll
+                for(int e = 0; e < N; ++e)
+                {
+                    part += exp_for(fib, x[u][e] - acc.top);
+                }
+                acc.sum += part;
             }
-            acc.sum += part;
         }
         for(int o = lpf >> 1; o > 0; o >>= 1)
         {
