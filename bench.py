@@ -70,7 +70,7 @@ NCU_DRAM_BYTES_PER_SLICE = {"flash_bwd_kernel<128>": 1563.0e6/128, "flash_fwd_ke
 # share of the backward tile task's device time spent in flash_bwd_kernel<128> itself
 # (the rest: mask classification, delta / accumulator preparation, dQ conversion), from
 # the ncu launch list of the config-3 workload (profiles/)
-NCU_BWD_KERNEL_SHARE = 0.887
+NCU_BWD_KERNEL_SHARE = 0.881
 
 
 def causal_flops(cfg):
