@@ -444,8 +444,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     {
                         continue;
                     }
-                    PROF_T(mt0);
-                    PROF_T(mt1);
                     PROF_T(mt2);
                     ok = mbar_wait_warp<LIMIT>(&sm.p_full[t], p_phase[t], abort_flag);
                     if(!ok) break;
@@ -469,10 +467,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                     __syncwarp();
                     PROF_T(mt4);
-                    PROF_ADD(8, mt0, mt1);      // (unused)
-                    PROF_ADD(9, mt1, mt2);      // issue 4 PV steps
-                    PROF_ADD(10, mt2, mt3);     // MMA thread: wait for P
-                    PROF_ADD(11, mt3, mt4);     // issue 4 PV steps
+                    PROF_ADD(10, mt2, mt3);     // issuing warp: wait for P
+                    PROF_ADD(11, mt3, mt4);     // issue 8 PV steps
 #ifdef NB200_PROF
                     if(lane == 0) atomicAdd(&g_prof[12], 1ull);
 #endif
