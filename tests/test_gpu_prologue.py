@@ -53,6 +53,7 @@ def test_against_reference_kernel_outputs(golden, tag):
     (12, 64, 1024, 1),       # config 2: 12 heads (rows are not whole 16-byte pieces)
     (2, 96, 33, 5),          # odd sizes: head/2 not a power of two
     (64, 256, 9, 1),         # one position needs more than the default chunk
+    (24, 64, 130, 2),        # a multiple of 8 that is not a power of two (three column blocks)
 ])
 def test_against_oracle_on_fresh_inputs(lead, head, seq, batch):
     rng = np.random.default_rng(lead*1000 + head + seq)
