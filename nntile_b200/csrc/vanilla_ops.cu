@@ -67,6 +67,21 @@ __device__ __forceinline__ void vstore(bf16 *p, const float (&v)[8])
 __device__ __forceinline__ float exp_for(const float *, float x) { return expf(x); }
 __device__ __forceinline__ float exp_for(const bf16 *, float x) { return __expf(x); }
 
+// exp(x - top) with `top` finite and fixed over many x: the bf16 form folds the
+// subtraction into the multiply by log2(e) (one fused multiply-add and one ex2)
+struct ExpShift
+{
+    float top, ntop_l2;
+    __device__ __forceinline__ explicit ExpShift(float t) : top(t), ntop_l2(-t*1.4426950408889634f) {}
+    __device__ __forceinline__ float operator()(const float *, float x) const { return expf(x - top); }
+    __device__ __forceinline__ float operator()(const bf16 *, float x) const
+    {
+        float y;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmaf(x, 1.4426950408889634f, ntop_l2)));
+        return y;
+    }
+};
+
 template<typename T>
 inline bool vec_ok(Index fibre_len, const void *a, const void *b = nullptr, const void *c = nullptr)
 {
@@ -310,12 +325,22 @@ maxsumexp_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ src, T 
 #pragma unroll
             for(int u = 0; u < U; ++u)
             {
-                ptop[u] = -CUDART_INF_F;
+                ptop[u] = x[u][0];
 #pragma unroll
-                for(int e = 0; e < N; ++e)
+                for(int e = 1; e < N; ++e)
                 {
-                    x[u][e] = isinf(x[u][e]) ? -CUDART_INF_F : x[u][e];     // +inf is skipped like -inf
                     ptop[u] = fmaxf(ptop[u], x[u][e]);
+                }
+                if(ptop[u] == CUDART_INF_F)
+                {
+                    // rare: +inf is skipped like -inf
+                    ptop[u] = -CUDART_INF_F;
+#pragma unroll
+                    for(int e = 0; e < N; ++e)
+                    {
+                        x[u][e] = isinf(x[u][e]) ? -CUDART_INF_F : x[u][e];
+                        ptop[u] = fmaxf(ptop[u], x[u][e]);
+                    }
                 }
                 top = fmaxf(top, ptop[u]);
             }
@@ -328,6 +353,7 @@ maxsumexp_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ src, T 
                 acc.sum *= exp_for(fib, acc.top - top);        // exp(-inf) = 0: empty pair
                 acc.top = top;
             }
+            const ExpShift shifted(acc.top);
 #pragma unroll
             for(int u = 0; u < U; ++u)
             {
@@ -339,7 +365,7 @@ maxsumexp_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ src, T 
 #pragma unroll
                 for(int e = 0; e < N; ++e)
                 {
-                    part += exp_for(fib, x[u][e] - acc.top);
+                    part += shifted(fib, x[u][e]);              // exp(-inf) = 0 drops masked values
                 }
                 acc.sum += part;
             }
