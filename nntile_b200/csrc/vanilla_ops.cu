@@ -436,17 +436,34 @@ softmax_inplace_m1_vec_kernel(Index n, Index k, int lpf, const T *__restrict__ m
     for(Index j = ((Index)blockIdx.x*blockDim.x + threadIdx.x)/lpf; j < n; j += groups)
     {
         const float top = ld(mse[2*j]), scale = alpha/ld(mse[2*j + 1]);
+        const ExpShift shifted(top);
         T *fib = dst + j*k;
-        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        const Index step = (Index)lpf*N;
+        // four pieces (four independent loads) per pass
+        for(Index l0 = (Index)sub*N; l0 < k; l0 += 4*step)
         {
-            float x[N];
-            vload(fib + l, x);
+            float x[4][N];
 #pragma unroll
-            for(int e = 0; e < N; ++e)
+            for(int u = 0; u < 4; ++u)
             {
-                x[e] = isinf(x[e]) ? 0.0f : exp_for(fib, x[e] - top)*scale;
+                if(l0 + u*step < k)
+                {
+                    vload(fib + l0 + u*step, x[u]);
+                }
             }
-            vstore(fib + l, x);
+#pragma unroll
+            for(int u = 0; u < 4; ++u)
+            {
+                if(l0 + u*step < k)
+                {
+#pragma unroll
+                    for(int e = 0; e < N; ++e)
+                    {
+                        x[u][e] = isinf(x[u][e]) ? 0.0f : shifted(fib, x[u][e])*scale;
+                    }
+                    vstore(fib + l0 + u*step, x[u]);
+                }
+            }
         }
     }
 }
@@ -550,16 +567,32 @@ add_slice_inplace_m1_vec_kernel(Index n, Index k, int lpf, float alpha, const T 
     {
         const float add = alpha*ld(src[j]);
         T *fib = dst + j*k;
-        for(Index l = (Index)sub*N; l < k; l += (Index)lpf*N)
+        const Index step = (Index)lpf*N;
+        // four pieces (four independent loads) per pass
+        for(Index l0 = (Index)sub*N; l0 < k; l0 += 4*step)
         {
-            float x[N];
-            vload(fib + l, x);
+            float x[4][N];
 #pragma unroll
-            for(int e = 0; e < N; ++e)
+            for(int u = 0; u < 4; ++u)
             {
-                x[e] = beta*x[e] + add;
+                if(l0 + u*step < k)
+                {
+                    vload(fib + l0 + u*step, x[u]);
+                }
             }
-            vstore(fib + l, x);
+#pragma unroll
+            for(int u = 0; u < 4; ++u)
+            {
+                if(l0 + u*step < k)
+                {
+#pragma unroll
+                    for(int e = 0; e < N; ++e)
+                    {
+                        x[u][e] = beta*x[u][e] + add;
+                    }
+                    vstore(fib + l0 + u*step, x[u]);
+                }
+            }
         }
     }
 }
