@@ -15,9 +15,9 @@
 // grouped-query entry points of the fused pair there is no K/V replication pass
 // (add_slice_inplace) left either.
 //
-// Two forms.  With lead a multiple of 8 a thread transposes an 8 x 8 block in
-// registers (transpose_in_reg_kernel below).  Otherwise (lead even, e.g. 12 heads)
-// one CTA handles `tp` consecutive (seq, batch) positions at a time: their
+// Two forms.  With lead a multiple of 4 a thread transposes an 8-row block of 8 (or,
+// for lead = 12, 20 ..., 4) columns in registers (transpose_in_reg_kernel below).
+// Otherwise (lead only even) one CTA handles `tp` consecutive (seq, batch) positions at a time: their
 // lead*head*tp source elements are one contiguous run, and for every value of
 // `lead` the tp*head destination elements are one contiguous run too.  The run is
 // staged in shared memory transposed, as tile[lead index][position*head + d], so
@@ -197,36 +197,78 @@ transpose_out_kernel(int lead, int head, Index npos, int tp, int swz, const bf16
     }
 }
 
-// ---- lead a multiple of 8: no staging at all.  The tensor is a [rows = position*head]
+// ---- lead a multiple of 4: no staging at all.  The tensor is a [rows = position*head]
 // x [lead] matrix to transpose; a thread takes an 8 x 8 block of it as eight 16-byte
 // loads (eight consecutive rows, which lie in one position because head is a
 // multiple of 8), transposes it in registers with byte permutes and writes eight
-// 16-byte pieces, one per lead index.  Consecutive threads take consecutive column
+// 16-byte pieces, one per lead index (8 x 4 blocks and 8-byte loads when lead is a
+// multiple of 4 only).  Consecutive threads take consecutive column
 // blocks of the same rows, then the next rows: a warp's loads cover whole 32-byte
 // sectors and its stores are runs of at least 128 bytes.
-__device__ __forceinline__ uint4 pro_column(const uint4 (&in)[8], int e)
+// 16-bit element e of each of the eight row pieces, in row order: CB = 8 (pieces of
+// 16 bytes) or 4 (pieces of 8 bytes, for head counts that are multiples of 4 only)
+template<int CB> struct ProPiece;
+template<> struct ProPiece<8>
 {
-    // 16-bit element e of each of the eight pieces, in order
+    typedef uint4 type;
+    static __device__ __forceinline__ uint32_t word(const uint4 &v, int i)
+    {
+        return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+    }
+    static __device__ __forceinline__ uint4 make(const uint32_t (&w)[4])
+    {
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template<> struct ProPiece<4>
+{
+    typedef uint2 type;
+    static __device__ __forceinline__ uint32_t word(const uint2 &v, int i)
+    {
+        return i == 0 ? v.x : v.y;
+    }
+    static __device__ __forceinline__ uint2 make(const uint32_t (&w)[2])
+    {
+        return make_uint2(w[0], w[1]);
+    }
+};
+
+// column e of an 8-row block: element e of each of the eight row pieces
+template<int CB>
+__device__ __forceinline__ uint4 pro_column(const typename ProPiece<CB>::type (&in)[8], int e)
+{
     const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
     uint32_t w[4];
 #pragma unroll
     for(int k = 0; k < 4; ++k)
     {
-        const uint32_t a = (e >> 1) == 0 ? in[2*k].x : (e >> 1) == 1 ? in[2*k].y
-                : (e >> 1) == 2 ? in[2*k].z : in[2*k].w;
-        const uint32_t b = (e >> 1) == 0 ? in[2*k + 1].x : (e >> 1) == 1 ? in[2*k + 1].y
-                : (e >> 1) == 2 ? in[2*k + 1].z : in[2*k + 1].w;
-        w[k] = __byte_perm(a, b, sel);
+        w[k] = __byte_perm(ProPiece<CB>::word(in[2*k], e >> 1), ProPiece<CB>::word(in[2*k + 1], e >> 1),
+                sel);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-template<int MODE>
+// row r of a CB-column block held as CB pieces of eight rows each
+template<int CB>
+__device__ __forceinline__ typename ProPiece<CB>::type pro_row(const uint4 (&in)[CB], int r)
+{
+    const uint32_t sel = (r & 1) ? 0x7632u : 0x5410u;
+    uint32_t w[CB/2];
+#pragma unroll
+    for(int k = 0; k < CB/2; ++k)
+    {
+        w[k] = __byte_perm(ProPiece<8>::word(in[2*k], r >> 1), ProPiece<8>::word(in[2*k + 1], r >> 1), sel);
+    }
+    return ProPiece<CB>::make(w);
+}
+
+template<int MODE, int CB>
 __global__ void __launch_bounds__(PRO_THREADS)
 transpose_in_reg_kernel(int lead, int head, Index nrows, const bf16 *__restrict__ aux0,
         const bf16 *__restrict__ aux1, const bf16 *__restrict__ src, bf16 *__restrict__ dst)
 {
-    const int pb = lead >> 3;
+    typedef typename ProPiece<CB>::type piece_t;
+    const int pb = lead/CB;
     const Index items = (nrows >> 3)*pb;
     for(Index v = (Index)blockIdx.x*PRO_THREADS + threadIdx.x; v < items;
             v += (Index)gridDim.x*PRO_THREADS)
@@ -234,8 +276,8 @@ transpose_in_reg_kernel(int lead, int head, Index nrows, const bf16 *__restrict_
         const Index rg = v/pb;
         const int p = (int)(v - rg*pb);
         const Index r0 = rg << 3;
-        const uint4 *g = reinterpret_cast<const uint4 *>(src + r0*lead + 8*p);
-        uint4 in[8];
+        const piece_t *g = reinterpret_cast<const piece_t *>(src + r0*lead + CB*p);
+        piece_t in[8];
 #pragma unroll
         for(int r = 0; r < 8; ++r)
         {
@@ -250,11 +292,11 @@ transpose_in_reg_kernel(int lead, int head, Index nrows, const bf16 *__restrict_
             sw[0] = sv.x; sw[1] = sv.y; cw[0] = cv.x; cw[1] = cv.y;
         }
 #pragma unroll
-        for(int e = 0; e < 8; ++e)
+        for(int e = 0; e < CB; ++e)
         {
-            const uint4 col = pro_column(in, e);
+            const uint4 col = pro_column<CB>(in, e);
             uint32_t w[4] = {col.x, col.y, col.z, col.w};
-            const int n = 8*p + e;
+            const int n = CB*p + e;
             if(MODE == PRO_ROPE)
             {
 #pragma unroll
@@ -289,10 +331,12 @@ transpose_in_reg_kernel(int lead, int head, Index nrows, const bf16 *__restrict_
     }
 }
 
+template<int CB>
 __global__ void __launch_bounds__(PRO_THREADS)
 transpose_out_reg_kernel(int lead, Index nrows, const bf16 *__restrict__ src, bf16 *__restrict__ dst)
 {
-    const int pb = lead >> 3;
+    typedef typename ProPiece<CB>::type piece_t;
+    const int pb = lead/CB;
     const Index items = (nrows >> 3)*pb;
     for(Index v = (Index)blockIdx.x*PRO_THREADS + threadIdx.x; v < items;
             v += (Index)gridDim.x*PRO_THREADS)
@@ -300,24 +344,24 @@ transpose_out_reg_kernel(int lead, Index nrows, const bf16 *__restrict__ src, bf
         const Index rg = v/pb;
         const int p = (int)(v - rg*pb);
         const Index r0 = rg << 3;
-        uint4 in[8];
+        uint4 in[CB];
 #pragma unroll
-        for(int e = 0; e < 8; ++e)
+        for(int e = 0; e < CB; ++e)
         {
-            in[e] = *reinterpret_cast<const uint4 *>(src + (Index)(8*p + e)*nrows + r0);
+            in[e] = *reinterpret_cast<const uint4 *>(src + (Index)(CB*p + e)*nrows + r0);
         }
-        uint4 *g = reinterpret_cast<uint4 *>(dst + r0*lead + 8*p);
+        piece_t *g = reinterpret_cast<piece_t *>(dst + r0*lead + CB*p);
 #pragma unroll
         for(int r = 0; r < 8; ++r)
         {
-            g[(Index)r*pb] = pro_column(in, r);
+            g[(Index)r*pb] = pro_row<CB>(in, r);
         }
     }
 }
 
-static unsigned pro_reg_grid(int lead, Index nrows)
+static unsigned pro_reg_grid(int lead, int cb, Index nrows)
 {
-    const Index items = (nrows >> 3)*(lead >> 3);
+    const Index items = (nrows >> 3)*(lead/cb);
     const Index blocks = (items + PRO_THREADS - 1)/PRO_THREADS;
     const Index cap = 148*16;
     return (unsigned)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
@@ -384,20 +428,29 @@ extern "C" int nntile_b200_transpose_rope_bf16(nntile_b200_stream_t stream, int6
     {
         return NNTILE_B200_E_ALIGN;
     }
-    if(lead % 8 == 0)
+    if(lead % 4 == 0)
     {
         const Index nrows = npos*head;
-        const unsigned grid = pro_reg_grid((int)lead, nrows);
-        if(sin)
+        const int cb = lead % 8 == 0 ? 8 : 4;
+        const unsigned grid = pro_reg_grid((int)lead, cb, nrows);
+        const bf16 *s0 = (const bf16 *)sin, *c0 = (const bf16 *)cos, *x = (const bf16 *)src;
+        bf16 *y = (bf16 *)dst;
+        cudaStream_t st_ = as_stream(stream);
+        if(sin && cb == 8)
         {
-            transpose_in_reg_kernel<PRO_ROPE><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead,
-                    (int)head, nrows, (const bf16 *)sin, (const bf16 *)cos, (const bf16 *)src,
-                    (bf16 *)dst);
+            transpose_in_reg_kernel<PRO_ROPE, 8><<<grid, PRO_THREADS, 0, st_>>>((int)lead, (int)head, nrows, s0, c0, x, y);
+        }
+        else if(sin)
+        {
+            transpose_in_reg_kernel<PRO_ROPE, 4><<<grid, PRO_THREADS, 0, st_>>>((int)lead, (int)head, nrows, s0, c0, x, y);
+        }
+        else if(cb == 8)
+        {
+            transpose_in_reg_kernel<PRO_PLAIN, 8><<<grid, PRO_THREADS, 0, st_>>>((int)lead, (int)head, nrows, nullptr, nullptr, x, y);
         }
         else
         {
-            transpose_in_reg_kernel<PRO_PLAIN><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead,
-                    (int)head, nrows, nullptr, nullptr, (const bf16 *)src, (bf16 *)dst);
+            transpose_in_reg_kernel<PRO_PLAIN, 4><<<grid, PRO_THREADS, 0, st_>>>((int)lead, (int)head, nrows, nullptr, nullptr, x, y);
         }
         return launch_status();
     }
@@ -432,12 +485,21 @@ extern "C" int nntile_b200_transpose_bias_bf16(nntile_b200_stream_t stream, int6
     {
         return NNTILE_B200_E_ALIGN;
     }
-    if(lead % 8 == 0)
+    if(lead % 4 == 0)
     {
         const Index nrows = npos*head;
-        transpose_in_reg_kernel<PRO_BIAS><<<pro_reg_grid((int)lead, nrows), PRO_THREADS, 0,
-                as_stream(stream)>>>((int)lead, (int)head, nrows, (const bf16 *)bias, nullptr,
-                (const bf16 *)src, (bf16 *)dst);
+        const int cb = lead % 8 == 0 ? 8 : 4;
+        const unsigned grid = pro_reg_grid((int)lead, cb, nrows);
+        if(cb == 8)
+        {
+            transpose_in_reg_kernel<PRO_BIAS, 8><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead,
+                    (int)head, nrows, (const bf16 *)bias, nullptr, (const bf16 *)src, (bf16 *)dst);
+        }
+        else
+        {
+            transpose_in_reg_kernel<PRO_BIAS, 4><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead,
+                    (int)head, nrows, (const bf16 *)bias, nullptr, (const bf16 *)src, (bf16 *)dst);
+        }
         return launch_status();
     }
     const ProPlan p = pro_plan((int)lead, (int)head, npos);
@@ -457,11 +519,21 @@ extern "C" int nntile_b200_transpose_heads_back_bf16(nntile_b200_stream_t stream
     if(lead == 0 || head == 0 || npos == 0) return NNTILE_B200_OK;
     if(!src || !dst) return NNTILE_B200_E_BADARG;
     if(!aligned16(dst) || !aligned16(src)) return NNTILE_B200_E_ALIGN;
-    if(lead % 8 == 0)
+    if(lead % 4 == 0)
     {
         const Index nrows = npos*head;
-        transpose_out_reg_kernel<<<pro_reg_grid((int)lead, nrows), PRO_THREADS, 0, as_stream(stream)>>>(
-                (int)lead, nrows, (const bf16 *)src, (bf16 *)dst);
+        const int cb = lead % 8 == 0 ? 8 : 4;
+        const unsigned grid = pro_reg_grid((int)lead, cb, nrows);
+        if(cb == 8)
+        {
+            transpose_out_reg_kernel<8><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead, nrows,
+                    (const bf16 *)src, (bf16 *)dst);
+        }
+        else
+        {
+            transpose_out_reg_kernel<4><<<grid, PRO_THREADS, 0, as_stream(stream)>>>((int)lead, nrows,
+                    (const bf16 *)src, (bf16 *)dst);
+        }
         return launch_status();
     }
     const ProPlan p = pro_plan((int)lead, (int)head, npos);
